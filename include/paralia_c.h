@@ -1,0 +1,209 @@
+/*
+ * paralia_c.h -- C ABI of libparalia.so (B200 / sm_100a build).
+ *
+ * Plain pointers and sizes only; no C++ or framework types cross this boundary.
+ * Every entry point returns a status code (PARALIA_OK == 0) instead of terminating
+ * the process, which is what the reference does on error
+ * (Library_scheduler/src/Functions/dgemm.cpp:42,92,399,450).
+ *
+ * Location ids follow the reference's convention
+ * (Benchmarking/CuCuBLAS/src/PARALia/dgemm_runner.cpp:55-57, Subkernel.cpp:46):
+ *   -1      pinned (or pinnable) host memory
+ *   0..G-1  memory of GPU <id>
+ *   PARALIA_LOC_AUTO  ask the CUDA runtime where the pointer lives, which is what the
+ *                     reference always does (CoCoGetPtrLoc, dgemm.cpp:356-363).
+ *
+ * All matrices are column-major, exactly as in BLAS / the reference.
+ */
+#ifndef PARALIA_C_H
+#define PARALIA_C_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PARALIA_MAX_UNITS 16
+#define PARALIA_LOC_HOST (-1)
+#define PARALIA_LOC_AUTO (-100)
+
+/* status codes */
+enum {
+  PARALIA_OK = 0,
+  PARALIA_ERR_INVALID_ARG = 1,
+  PARALIA_ERR_OUT_OF_MEMORY = 2,
+  PARALIA_ERR_CUDA = 3,
+  PARALIA_ERR_TIMEOUT = 4,
+  PARALIA_ERR_NO_PEER_ACCESS = 5,
+  PARALIA_ERR_DB_MISSING = 6,
+  PARALIA_ERR_NO_DEVICE = 7,
+  PARALIA_ERR_UNSUPPORTED = 8
+};
+
+/*
+ * Caller-fixed control values: the C form of the "predefined" autotune controller that
+ * the reference passes to its ...Controled entry points
+ * (Library_scheduler/src/Functions/dgemm.cpp:697-705, fields Autotuner.hpp:121-149;
+ * CLI meaning Benchmarking/CuCuBLAS/src/testing.cpp:280-308).
+ * A field <= 0 (or a NULL ctl) means "let the autotuner choose".
+ */
+typedef struct paralia_ctl {
+  int64_t T;                                   /* tile edge in elements                */
+  int32_t active_unit_num;                     /* number of GPUs to use                */
+  int32_t active_unit_id_list[PARALIA_MAX_UNITS]; /* their ids, grid order (r*D2+c)    */
+  int64_t cache_limit;                         /* bytes of tile cache per GPU          */
+  int32_t exec_streams;                        /* compute streams per GPU (default 4;
+                                                  reference MAX_BACKEND_L=8,
+                                                  CMakeLists.txt:69)                   */
+  int32_t flags;                               /* PARALIA_FLAG_* below                 */
+} paralia_ctl;
+
+#define PARALIA_FLAG_NO_PEER_FETCH 1  /* every GPU fetches host tiles itself            */
+#define PARALIA_FLAG_KEEP_PINNED   2  /* leave host operands registered after the call  */
+#define PARALIA_FLAG_NO_METADATA_REUSE 4 /* rebuild the plan even for a known signature */
+
+/*
+ * What a call did: the POD form of the ATC object the reference returns
+ * (dgemm.cpp:689-693; fields read by callers: dgemm_runner.cpp:26-33,140,147).
+ */
+typedef struct paralia_report {
+  int64_t T;
+  int32_t active_unit_num;
+  int32_t active_unit_id_list[PARALIA_MAX_UNITS];
+  double  active_unit_score[PARALIA_MAX_UNITS];
+  int64_t cache_limit;
+  int64_t subkernel_num;
+  int32_t subkernels_per_unit[PARALIA_MAX_UNITS];
+  double  pred_t;            /* model-predicted seconds                         */
+  double  pred_J;            /* always 0: energy modelling is not built         */
+  double  T_slowdowns[6];    /* aggregate, imbalance, remainder, small, sknum, big
+                                (Autotuner.cpp:562-603)                          */
+  /* measured */
+  double  device_ms;         /* first enqueue -> last write-back, CUDA events,
+                                max over the GPUs used                           */
+  double  host_ms;           /* wall clock of the whole call                    */
+  double  plan_ms;           /* autotune + plan construction                    */
+  double  pin_ms;            /* host registration inside the call               */
+  double  alloc_ms;          /* tile-cache slab (re)allocation                  */
+  int64_t h2d_bytes, d2h_bytes, p2p_bytes, d2d_bytes;
+  int64_t kernel_launches;   /* launches of this library's own kernels          */
+  int32_t metadata_reused;   /* 1 if the plan came from the signature cache     */
+  int32_t grid_d1, grid_d2;  /* device grid D1_parts x D2_parts                 */
+} paralia_report;
+
+/* ---- library life cycle ---------------------------------------------------------- */
+/* Discover GPUs, enable peer access between every pair (reference: CoCoEnableLinks,
+ * dgemm.cpp:423). Idempotent; every other entry point calls it on first use. */
+int PARALiA_init(void);
+/* Free every slab, stream, event and cached plan. */
+int PARALiA_finalize(void);
+/* Number of GPUs the library sees (reference: compile-time LOC_NUM-1). */
+int PARALiA_device_count(void);
+/* Text of the last error on the calling thread. */
+const char* PARALiA_last_error(void);
+/* Replaces PARALiADevCacheFree (Library_scheduler/src/Subkernel.cpp:488-495):
+ * frees the tile-cache slab of one location and drops it from cached plans. */
+int PARALiA_dev_cache_free(int loc);
+
+/* ---- the four routines of the hot path -------------------------------------------- */
+/* Replaces PARALiADgemm / PARALiADgemmControled (PARALiA.hpp:33-38,
+ * dgemm.cpp:318-705): C <- alpha*op(A)*op(B) + beta*C, FP64. Blocking: returns after C
+ * is completely written (dgemm.cpp:596-597). */
+int PARALiA_dgemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K,
+                  double alpha, const double* A, int64_t ldA, int locA,
+                  const double* B, int64_t ldB, int locB,
+                  double beta, double* C, int64_t ldC, int locC,
+                  const paralia_ctl* ctl, paralia_report* out);
+
+/* Replaces PARALiASgemm / PARALiASgemmControled (PARALiA.hpp:41-46,
+ * Library_scheduler/src/Functions/sgemm.cpp:296-...): FP32 via a 3xTF32 split. */
+int PARALiA_sgemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K,
+                  float alpha, const float* A, int64_t ldA, int locA,
+                  const float* B, int64_t ldB, int locB,
+                  float beta, float* C, int64_t ldC, int locC,
+                  const paralia_ctl* ctl, paralia_report* out);
+
+/* Replaces PARALiADaxpy / PARALiADaxpyControled (PARALiA.hpp:56-61,
+ * Library_scheduler/src/Functions/daxpy.cpp:200-469): y <- alpha*x + y. */
+int PARALiA_daxpy(int64_t N, double alpha, const double* x, int64_t incx, int locx,
+                  double* y, int64_t incy, int locy,
+                  const paralia_ctl* ctl, paralia_report* out);
+
+/* Replaces PARALiADdot / PARALiADdotControled (PARALiA.hpp:64-69,
+ * Library_scheduler/src/Functions/ddot.cpp:201-469): *result += sum_i x_i*y_i.
+ * As in the reference the partial sums are ADDED to *result, which the caller zeroes
+ * (ddot.cpp:431, Benchmarking/CuCuBLAS/src/PARALia/ddot_runner.cpp:45). The sum order
+ * is fixed (tile order, then a fixed tree inside a tile), so results are bit-reproducible. */
+int PARALiA_ddot(int64_t N, const double* x, int64_t incx, int locx,
+                 const double* y, int64_t incy, int locy, double* result,
+                 const paralia_ctl* ctl, paralia_report* out);
+
+/* ---- per-tile kernels on device-resident data ---------------------------------------
+ * What the reference reaches through backend_run_operation(params, "Dgemm"|"Sgemm"|
+ * "Daxpy"|"Ddot", queue) (Library_scheduler/src/Subkernel.cpp:168,228; parameter blocks
+ * dgemm.cpp:181-197, daxpy.cpp:62-69, ddot.cpp:62-70) and the microbenchmarks time
+ * (Database_builder/CuCuBLAS/src/dgemm_microbench.cu:141-142). All pointers are device
+ * pointers on GPU `dev`; `stream` is a cudaStream_t (NULL = the legacy default stream).
+ * Asynchronous: the caller synchronises the stream. */
+int PARALiA_tile_dgemm(int dev, void* stream, char TransA, char TransB,
+                       int64_t M, int64_t N, int64_t K, double alpha,
+                       const double* A, int64_t ldA, const double* B, int64_t ldB,
+                       double beta, double* C, int64_t ldC);
+int PARALiA_tile_sgemm(int dev, void* stream, char TransA, char TransB,
+                       int64_t M, int64_t N, int64_t K, float alpha,
+                       const float* A, int64_t ldA, const float* B, int64_t ldB,
+                       float beta, float* C, int64_t ldC);
+int PARALiA_tile_daxpy(int dev, void* stream, int64_t N, double alpha,
+                       const double* x, int64_t incx, double* y, int64_t incy);
+/* `partials` is device scratch of PARALiA_tile_ddot_scratch_bytes(N) bytes; the result
+ * (one double) is written to device memory at `result_dev`. */
+int64_t PARALiA_tile_ddot_scratch_bytes(int64_t N);
+int PARALiA_tile_ddot(int dev, void* stream, int64_t N,
+                      const double* x, int64_t incx, const double* y, int64_t incy,
+                      double* partials, double* result_dev);
+
+/* ---- memory and input helpers (reference: CoCoMalloc/CoCoFree/CoCoVecInit/CoCoMemcpy,
+ * used at dgemm_runner.cpp:55-69,77) ------------------------------------------------- */
+int PARALiA_malloc(void** ptr, int64_t bytes, int loc);   /* loc -1: pinned host     */
+int PARALiA_free(void* ptr, int loc);
+int PARALiA_memcpy(void* dst, int loc_dst, const void* src, int loc_src, int64_t bytes);
+/* Counter-based generators: element i of a buffer depends only on (seed, i), so the
+ * same bits come out on the host and on any GPU. dist: 0 = uniform[-1,1), 1 = normal(0,1). */
+int PARALiA_fill_f64(double* ptr, int64_t n, uint64_t seed, int dist, int loc);
+int PARALiA_fill_f32(float* ptr, int64_t n, uint64_t seed, int dist, int loc);
+
+/* ---- autotuner / plan introspection ---------------------------------------------------
+ * Runs only the model (reference: ATC::autotune_problem, Autotuner.cpp:279-560; the
+ * autotune-only CLI Benchmarking/CuCuBLAS/src/PARALia/dgemm_predictor.cpp:16-93).
+ * Needs no GPU when ctl fixes active_unit_num. */
+int PARALiA_autotune_gemm(int elem_size, char TransA, char TransB,
+                          int64_t M, int64_t N, int64_t K, int locA, int locB, int locC,
+                          const paralia_ctl* ctl, paralia_report* out);
+/* Tile-size score of one candidate T (Autotuner.cpp:571-603); slowdowns[6]. */
+int PARALiA_tile_slowdowns(int64_t M, int64_t N, int64_t K, int64_t T, int active_units,
+                           double* slowdowns);
+/* Subkernel -> unit assignment of the 2D block distribution
+ * (Autotuner/src/Subkernel_distributions.cpp:315-485). sk_unit[sk_id] receives the
+ * index (into the active unit list) that owns subkernel sk_id = mi*Nt*Kt + ni*Kt + ki;
+ * d1/d2 receive the device grid. */
+int PARALiA_distribute_2d(int units, int Mt, int Nt, int Kt, int32_t* sk_unit,
+                          int32_t* d1, int32_t* d2);
+/* Load / replace the calibration database directory (lookup tables + link models). */
+int PARALiA_load_database(const char* dir);
+
+/* ---- calibration microbenchmarks (reference: Database_builder/CuCuBLAS/src/
+ * dgemm_microbench.cu, transfer_link_microbench.cu) ------------------------------------ */
+/* Register-only FP64 tensor-core loop; returns sustained TFLOP/s of GPU `dev`.
+ * shape: 884, 1684, 1688 or 16816 (mma.sync m/n/k). */
+int PARALiA_bench_dmma_peak(int dev, int shape, int iters, double* tflops);
+/* Time `reps` launches of the tile DGEMM on square T; returns mean seconds. */
+int PARALiA_bench_tile_dgemm(int dev, char TransA, char TransB, int64_t T, int reps,
+                             double* mean_s);
+/* Time a strided 2-D tile copy dim x dim doubles src_loc -> dst_loc; mean seconds. */
+int PARALiA_bench_link(int dst_loc, int src_loc, int64_t dim, int reps, double* mean_s);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PARALIA_C_H */

@@ -1,0 +1,447 @@
+// extern "C" layer of libparalia.so: every symbol declared in include/paralia_c.h.
+#include <algorithm>
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+#include <thread>
+#include <vector>
+
+#include "autotune.hpp"
+#include "dgemm_tile.cuh"
+#include "exec.hpp"
+#include "level1.cuh"
+#include "paralia_rng.h"
+#include "runtime.hpp"
+#include "sgemm_tile.cuh"
+
+using namespace paralia;
+
+namespace {
+
+int norm_t(char t) { return (t == 'T' || t == 't' || t == 'C' || t == 'c') ? 1 : 0; }
+bool valid_t(char t) {
+  return t == 'N' || t == 'n' || t == 'T' || t == 't' || t == 'C' || t == 'c';
+}
+
+int setup_device(int dev) {
+  Runtime& rt = Runtime::get();
+  PL_TRY(rt.init());
+  PL_TRY(rt.ensure_device(dev));
+  PL_CUDA(cudaSetDevice(dev));
+  return PARALIA_OK;
+}
+
+template <typename F>
+void parallel_fill(int64_t n, F f) {
+  unsigned hw = std::thread::hardware_concurrency();
+  int nt = (int)std::min<int64_t>(hw ? hw : 1, std::max<int64_t>(1, n / (1 << 16)));
+  if (nt <= 1) { f(0, n); return; }
+  std::vector<std::thread> th;
+  const int64_t chunk = (n + nt - 1) / nt;
+  for (int t = 0; t < nt; ++t) {
+    const int64_t lo = t * chunk, hi = std::min<int64_t>(n, lo + chunk);
+    if (lo >= hi) break;
+    th.emplace_back([=] { f(lo, hi); });
+  }
+  for (auto& t : th) t.join();
+}
+
+}  // namespace
+
+extern "C" {
+
+int PARALiA_init(void) { return Runtime::get().init(); }
+int PARALiA_finalize(void) { return Runtime::get().finalize(); }
+int PARALiA_device_count(void) {
+  Runtime& rt = Runtime::get();
+  if (rt.init() != PARALIA_OK) return 0;
+  return rt.device_count();
+}
+const char* PARALiA_last_error(void) { return last_error_cstr(); }
+
+int PARALiA_dev_cache_free(int loc) {
+  Runtime& rt = Runtime::get();
+  PL_TRY(rt.init());
+  std::lock_guard<std::mutex> lk(rt.call_mutex());
+  DeviceGuard guard;
+  if (loc == -1) return PARALIA_OK;  // the host keeps no cache in this build
+  return rt.free_slab(loc);
+}
+
+int PARALiA_dgemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, double alpha,
+                  const double* A, int64_t ldA, int locA, const double* B, int64_t ldB, int locB,
+                  double beta, double* C, int64_t ldC, int locC, const paralia_ctl* ctl,
+                  paralia_report* out) {
+  return exec_dgemm(TransA, TransB, M, N, K, alpha, A, ldA, locA, B, ldB, locB, beta, C, ldC, locC,
+                    ctl, out);
+}
+
+int PARALiA_sgemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, float alpha,
+                  const float* A, int64_t ldA, int locA, const float* B, int64_t ldB, int locB,
+                  float beta, float* C, int64_t ldC, int locC, const paralia_ctl* ctl,
+                  paralia_report* out) {
+  return exec_sgemm(TransA, TransB, M, N, K, alpha, A, ldA, locA, B, ldB, locB, beta, C, ldC, locC,
+                    ctl, out);
+}
+
+int PARALiA_daxpy(int64_t N, double alpha, const double* x, int64_t incx, int locx, double* y,
+                  int64_t incy, int locy, const paralia_ctl* ctl, paralia_report* out) {
+  return exec_daxpy(N, alpha, x, incx, locx, y, incy, locy, ctl, out);
+}
+
+int PARALiA_ddot(int64_t N, const double* x, int64_t incx, int locx, const double* y, int64_t incy,
+                 int locy, double* result, const paralia_ctl* ctl, paralia_report* out) {
+  return exec_ddot(N, x, incx, locx, y, incy, locy, result, ctl, out);
+}
+
+// ------------------------------ per-tile kernels ------------------------------
+
+int PARALiA_tile_dgemm(int dev, void* stream, char TransA, char TransB, int64_t M, int64_t N,
+                       int64_t K, double alpha, const double* A, int64_t ldA, const double* B,
+                       int64_t ldB, double beta, double* C, int64_t ldC) {
+  if (!valid_t(TransA) || !valid_t(TransB))
+    return fail(PARALIA_ERR_INVALID_ARG, "transpose flag is not N or T");
+  if (M < 0 || N < 0 || K < 0 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX)
+    return fail(PARALIA_ERR_INVALID_ARG, "dimension out of range");
+  if (M == 0 || N == 0) return PARALIA_OK;
+  const int ta = norm_t(TransA), tb = norm_t(TransB);
+  const int64_t a_rows = ta ? K : M, a_cols = ta ? M : K, b_rows = tb ? N : K, b_cols = tb ? K : N;
+  if (ldA < std::max<int64_t>(1, a_rows) || ldB < std::max<int64_t>(1, b_rows) ||
+      ldC < std::max<int64_t>(1, M))
+    return fail(PARALIA_ERR_INVALID_ARG, "leading dimension smaller than the stored row count");
+  DeviceGuard guard;
+  PL_TRY(setup_device(dev));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool tma = K > 0 && tma_addressable(A, ldA, 8) && tma_addressable(B, ldB, 8);
+  if (!tma) {
+    PL_CUDA(launch_dgemm_generic(ta ? 'T' : 'N', tb ? 'T' : 'N', (int)M, (int)N, (int)K, alpha, A,
+                                 ldA, B, ldB, beta, C, ldC, s));
+    return PARALIA_OK;
+  }
+  CUtensorMap mapA, mapB;
+  PL_TRY(make_tensor_map(&mapA, A, 8, a_rows, a_cols, 1, ldA * 8, (uint64_t)ldA * a_cols * 8, 16,
+                         ta ? 128 : 16));
+  PL_TRY(make_tensor_map(&mapB, B, 8, b_rows, b_cols, 1, ldB * 8, (uint64_t)ldB * b_cols * 8, 16,
+                         tb ? 16 : 128));
+  DgemmArgs args;
+  memset(&args, 0, sizeof(args));
+  args.C = C;
+  args.ldc = ldC;
+  args.alpha = alpha;
+  args.beta_c = beta;
+  args.M = (int32_t)M;
+  args.N = (int32_t)N;
+  args.vec_ok = tma_addressable(C, ldC, 8) ? 1 : 0;
+  args.status = Runtime::get().dev(dev).status_dev;
+  args.nparts = 1;
+  args.parts[0].klen = (int32_t)K;
+  PL_CUDA(launch_dgemm_tile(mapA, mapB, args, ta != 0, tb == 0, s));
+  return PARALIA_OK;
+}
+
+int PARALiA_tile_sgemm(int dev, void* stream, char TransA, char TransB, int64_t M, int64_t N,
+                       int64_t K, float alpha, const float* A, int64_t ldA, const float* B,
+                       int64_t ldB, float beta, float* C, int64_t ldC) {
+  return exec_tile_sgemm(dev, stream, TransA, TransB, M, N, K, alpha, A, ldA, B, ldB, beta, C, ldC);
+}
+
+int PARALiA_tile_daxpy(int dev, void* stream, int64_t N, double alpha, const double* x,
+                       int64_t incx, double* y, int64_t incy) {
+  if (N < 0 || incx <= 0 || incy <= 0) return fail(PARALIA_ERR_INVALID_ARG, "bad N or increment");
+  DeviceGuard guard;
+  PL_TRY(setup_device(dev));
+  PL_CUDA(launch_daxpy(N, alpha, x, incx, y, incy, static_cast<cudaStream_t>(stream), nullptr));
+  return PARALIA_OK;
+}
+
+int64_t PARALiA_tile_ddot_scratch_bytes(int64_t N) {
+  return (int64_t)l1_grid_blocks(N > 0 ? N : 1) * (int64_t)sizeof(double);
+}
+
+int PARALiA_tile_ddot(int dev, void* stream, int64_t N, const double* x, int64_t incx,
+                      const double* y, int64_t incy, double* partials, double* result_dev) {
+  if (N < 0 || incx <= 0 || incy <= 0) return fail(PARALIA_ERR_INVALID_ARG, "bad N or increment");
+  if (!partials || !result_dev) return fail(PARALIA_ERR_INVALID_ARG, "NULL scratch or result");
+  DeviceGuard guard;
+  PL_TRY(setup_device(dev));
+  PL_CUDA(launch_ddot(N, x, incx, y, incy, partials, result_dev, static_cast<cudaStream_t>(stream),
+                      nullptr));
+  return PARALIA_OK;
+}
+
+// ------------------------------ memory and inputs ------------------------------
+
+int PARALiA_malloc(void** ptr, int64_t bytes, int loc) {
+  if (!ptr || bytes < 0) return fail(PARALIA_ERR_INVALID_ARG, "bad malloc arguments");
+  *ptr = nullptr;
+  if (bytes == 0) return PARALIA_OK;
+  Runtime& rt = Runtime::get();
+  PL_TRY(rt.init());
+  DeviceGuard guard;
+  if (loc == -1) {
+    cudaError_t e = cudaHostAlloc(ptr, (size_t)bytes, cudaHostAllocPortable);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return fail(PARALIA_ERR_OUT_OF_MEMORY, "pinned host allocation of %lld bytes failed: %s",
+                  (long long)bytes, cudaGetErrorString(e));
+    }
+    return PARALIA_OK;
+  }
+  if (loc < 0 || loc >= rt.device_count())
+    return fail(PARALIA_ERR_INVALID_ARG, "location id %d is not valid", loc);
+  PL_CUDA(cudaSetDevice(loc));
+  cudaError_t e = cudaMalloc(ptr, (size_t)bytes);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(PARALIA_ERR_OUT_OF_MEMORY, "GPU %d allocation of %lld bytes failed: %s", loc,
+                (long long)bytes, cudaGetErrorString(e));
+  }
+  return PARALIA_OK;
+}
+
+int PARALiA_free(void* ptr, int loc) {
+  if (!ptr) return PARALIA_OK;
+  DeviceGuard guard;
+  if (loc == -1) PL_CUDA(cudaFreeHost(ptr));
+  else {
+    PL_CUDA(cudaSetDevice(loc));
+    PL_CUDA(cudaFree(ptr));
+  }
+  return PARALIA_OK;
+}
+
+int PARALiA_memcpy(void* dst, int loc_dst, const void* src, int loc_src, int64_t bytes) {
+  (void)loc_dst;
+  (void)loc_src;
+  if (bytes < 0) return fail(PARALIA_ERR_INVALID_ARG, "negative byte count");
+  if (bytes == 0) return PARALIA_OK;
+  PL_TRY(Runtime::get().init());
+  PL_CUDA(cudaMemcpy(dst, src, (size_t)bytes, cudaMemcpyDefault));
+  return PARALIA_OK;
+}
+
+int PARALiA_fill_f64(double* ptr, int64_t n, uint64_t seed, int dist, int loc) {
+  if (n < 0 || (dist != 0 && dist != 1)) return fail(PARALIA_ERR_INVALID_ARG, "bad fill arguments");
+  if (n == 0) return PARALIA_OK;
+  if (loc == -1) {
+    if (dist == 0)
+      parallel_fill(n, [=](int64_t lo, int64_t hi) {
+        for (int64_t i = lo; i < hi; ++i) ptr[i] = paralia_uniform_f64(seed, (uint64_t)i);
+      });
+    else
+      parallel_fill(n, [=](int64_t lo, int64_t hi) {
+        for (int64_t i = lo; i < hi; ++i) ptr[i] = paralia_normal_f64(seed, (uint64_t)i);
+      });
+    return PARALIA_OK;
+  }
+  DeviceGuard guard;
+  PL_TRY(setup_device(loc));
+  PL_CUDA(launch_fill_f64(ptr, n, seed, dist, nullptr));
+  PL_CUDA(cudaDeviceSynchronize());
+  return PARALIA_OK;
+}
+
+int PARALiA_fill_f32(float* ptr, int64_t n, uint64_t seed, int dist, int loc) {
+  if (n < 0 || (dist != 0 && dist != 1)) return fail(PARALIA_ERR_INVALID_ARG, "bad fill arguments");
+  if (n == 0) return PARALIA_OK;
+  if (loc == -1) {
+    if (dist == 0)
+      parallel_fill(n, [=](int64_t lo, int64_t hi) {
+        for (int64_t i = lo; i < hi; ++i) ptr[i] = paralia_uniform_f32(seed, (uint64_t)i);
+      });
+    else
+      parallel_fill(n, [=](int64_t lo, int64_t hi) {
+        for (int64_t i = lo; i < hi; ++i) ptr[i] = (float)paralia_normal_f64(seed, (uint64_t)i);
+      });
+    return PARALIA_OK;
+  }
+  DeviceGuard guard;
+  PL_TRY(setup_device(loc));
+  PL_CUDA(launch_fill_f32(ptr, n, seed, dist, nullptr));
+  PL_CUDA(cudaDeviceSynchronize());
+  return PARALIA_OK;
+}
+
+// ------------------------------ autotuner ------------------------------
+
+int PARALiA_autotune_gemm(int elem_size, char TransA, char TransB, int64_t M, int64_t N, int64_t K,
+                          int locA, int locB, int locC, const paralia_ctl* ctl,
+                          paralia_report* out) {
+  if (elem_size != 4 && elem_size != 8)
+    return fail(PARALIA_ERR_INVALID_ARG, "element size must be 4 or 8");
+  if (!valid_t(TransA) || !valid_t(TransB))
+    return fail(PARALIA_ERR_INVALID_ARG, "transpose flag is not N or T");
+  int ngpu = 0;
+  if (!(ctl && ctl->active_unit_num > 0)) {
+    Runtime& rt = Runtime::get();
+    PL_TRY(rt.init());
+    ngpu = rt.device_count();
+  } else {
+    // a fixed unit list needs no GPU: size the default link table from the list
+    for (int i = 0; i < ctl->active_unit_num && i < PARALIA_MAX_UNITS; ++i)
+      ngpu = std::max(ngpu, ctl->active_unit_id_list[i] + 1);
+    ngpu = std::max(ngpu, std::max(locA, std::max(locB, locC)) + 1);
+  }
+  if (model_db().link.empty() || (int)model_db().link.size() < ngpu + 1)
+    reset_database_defaults(ngpu);
+  GemmModelInput in;
+  in.esz = elem_size;
+  in.ta = norm_t(TransA) ? 'T' : 'N';
+  in.tb = norm_t(TransB) ? 'T' : 'N';
+  in.M = M; in.N = N; in.K = K;
+  in.locA = locA; in.locB = locB; in.locC = locC;
+  in.func = elem_size == 8 ? "Dgemm" : "Sgemm";
+  return autotune_gemm(in, ngpu, ctl, out);
+}
+
+int PARALiA_tile_slowdowns(int64_t M, int64_t N, int64_t K, int64_t T, int active_units,
+                           double* slowdowns) {
+  if (M <= 0 || N <= 0 || K <= 0 || T <= 0 || active_units <= 0 || !slowdowns)
+    return fail(PARALIA_ERR_INVALID_ARG, "bad tile_slowdowns arguments");
+  tile_slowdowns(M, N, K, T, active_units, tune_constants(), slowdowns);
+  return PARALIA_OK;
+}
+
+int PARALiA_distribute_2d(int units, int Mt, int Nt, int Kt, int32_t* sk_unit, int32_t* d1,
+                          int32_t* d2) {
+  if (units <= 0 || Mt <= 0 || Nt <= 0 || Kt <= 0 || !sk_unit)
+    return fail(PARALIA_ERR_INVALID_ARG, "bad distribute_2d arguments");
+  std::vector<std::vector<int>> lists;
+  int g1 = 1, g2 = 1;
+  const int active = distribute_subkernels_2d(units, Mt, Nt, Kt, &lists, &g1, &g2);
+  if (active < 0) return fail(PARALIA_ERR_INVALID_ARG, "distribution failed");
+  for (int i = 0; i < Mt * Nt * Kt; ++i) sk_unit[i] = -1;
+  for (int u = 0; u < active; ++u)
+    for (int sk : lists[u]) sk_unit[sk] = u;
+  if (d1) *d1 = g1;
+  if (d2) *d2 = g2;
+  return PARALIA_OK;
+}
+
+int PARALiA_load_database(const char* dir) {
+  if (model_db().link.empty()) {
+    int n = 8;
+    Runtime& rt = Runtime::get();
+    if (rt.init() == PARALIA_OK) n = rt.device_count();
+    reset_database_defaults(n);
+  }
+  return load_database(dir);
+}
+
+// ------------------------------ calibration ------------------------------
+
+int PARALiA_bench_dmma_peak(int dev, int shape, int iters, double* tflops) {
+  if (!tflops || iters <= 0) return fail(PARALIA_ERR_INVALID_ARG, "bad bench arguments");
+  DeviceGuard guard;
+  PL_TRY(setup_device(dev));
+  int sms = 0;
+  PL_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const int blocks = sms * 2;  // 2 x 256 threads per SM: four warps per scheduler
+  double* sink = nullptr;
+  PL_CUDA(cudaMalloc(&sink, sizeof(double)));
+  cudaEvent_t e0, e1;
+  PL_CUDA(cudaEventCreate(&e0));
+  PL_CUDA(cudaEventCreate(&e1));
+  PL_CUDA(launch_dmma_peak(shape, iters / 4 + 1, blocks, sink, nullptr));  // warm-up
+  PL_CUDA(cudaEventRecord(e0, nullptr));
+  PL_CUDA(launch_dmma_peak(shape, iters, blocks, sink, nullptr));
+  PL_CUDA(cudaEventRecord(e1, nullptr));
+  PL_CUDA(cudaEventSynchronize(e1));
+  float ms = 0.f;
+  PL_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+  double flop_per_mma = 0;
+  switch (shape) {
+    case 884: flop_per_mma = 2.0 * 8 * 8 * 4; break;
+    case 1684: flop_per_mma = 2.0 * 16 * 8 * 4; break;
+    case 1688: flop_per_mma = 2.0 * 16 * 8 * 8; break;
+    case 16816: flop_per_mma = 2.0 * 16 * 8 * 16; break;
+  }
+  const double total = flop_per_mma * 8.0 /*chains*/ * (double)iters * 8.0 /*warps*/ * blocks;
+  *tflops = total / (ms * 1e-3) / 1e12;
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  cudaFree(sink);
+  return PARALIA_OK;
+}
+
+int PARALiA_bench_tile_dgemm(int dev, char TransA, char TransB, int64_t T, int reps,
+                             double* mean_s) {
+  if (!mean_s || reps <= 0 || T <= 0) return fail(PARALIA_ERR_INVALID_ARG, "bad bench arguments");
+  DeviceGuard guard;
+  PL_TRY(setup_device(dev));
+  const size_t n = (size_t)T * T;
+  double *A = nullptr, *B = nullptr, *C = nullptr;
+  PL_CUDA(cudaMalloc(&A, n * 8));
+  PL_CUDA(cudaMalloc(&B, n * 8));
+  PL_CUDA(cudaMalloc(&C, n * 8));
+  PL_CUDA(launch_fill_f64(A, n, 42, 0, nullptr));
+  PL_CUDA(launch_fill_f64(B, n, 43, 0, nullptr));
+  PL_CUDA(launch_fill_f64(C, n, 44, 0, nullptr));
+  cudaEvent_t e0, e1;
+  PL_CUDA(cudaEventCreate(&e0));
+  PL_CUDA(cudaEventCreate(&e1));
+  int rc = PARALIA_OK;
+  for (int i = 0; i < 2 && rc == PARALIA_OK; ++i)
+    rc = PARALiA_tile_dgemm(dev, nullptr, TransA, TransB, T, T, T, 1.0, A, T, B, T, 0.5, C, T);
+  if (rc == PARALIA_OK) {
+    PL_CUDA(cudaSetDevice(dev));
+    PL_CUDA(cudaEventRecord(e0, nullptr));
+    for (int i = 0; i < reps && rc == PARALIA_OK; ++i)
+      rc = PARALiA_tile_dgemm(dev, nullptr, TransA, TransB, T, T, T, 1.0, A, T, B, T, 0.5, C, T);
+    PL_CUDA(cudaSetDevice(dev));
+    PL_CUDA(cudaEventRecord(e1, nullptr));
+    PL_CUDA(cudaEventSynchronize(e1));
+    float ms = 0.f;
+    PL_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+    *mean_s = ms * 1e-3 / reps;
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  cudaFree(A);
+  cudaFree(B);
+  cudaFree(C);
+  if (rc == PARALIA_OK) rc = Runtime::get().check_status(dev);
+  return rc;
+}
+
+int PARALiA_bench_link(int dst_loc, int src_loc, int64_t dim, int reps, double* mean_s) {
+  if (!mean_s || reps <= 0 || dim <= 0) return fail(PARALIA_ERR_INVALID_ARG, "bad bench arguments");
+  Runtime& rt = Runtime::get();
+  PL_TRY(rt.init());
+  if (dst_loc == src_loc) return fail(PARALIA_ERR_INVALID_ARG, "source and destination are the same");
+  DeviceGuard guard;
+  // A dim x dim tile cut out of a (dim+64)-row matrix: the strided 2-D copy the scheduler issues.
+  const int64_t ld = dim + 64;
+  const int64_t bytes = ld * dim * 8;
+  void *src = nullptr, *dst = nullptr;
+  PL_TRY(PARALiA_malloc(&src, bytes, src_loc));
+  int rc = PARALiA_malloc(&dst, bytes, dst_loc);
+  if (rc != PARALIA_OK) { PARALiA_free(src, src_loc); return rc; }
+  const int drive = dst_loc >= 0 ? dst_loc : src_loc;
+  rc = rt.ensure_device(drive);
+  if (rc == PARALIA_OK) {
+    cudaSetDevice(drive);
+    cudaStream_t s = dst_loc >= 0 ? (src_loc >= 0 ? rt.dev(drive).p2p : rt.dev(drive).h2d)
+                                  : rt.dev(drive).d2h;
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    cudaMemcpy2DAsync(dst, ld * 8, src, ld * 8, dim * 8, dim, cudaMemcpyDefault, s);  // warm-up
+    cudaEventRecord(e0, s);
+    for (int i = 0; i < reps; ++i)
+      cudaMemcpy2DAsync(dst, ld * 8, src, ld * 8, dim * 8, dim, cudaMemcpyDefault, s);
+    cudaEventRecord(e1, s);
+    cudaError_t e = cudaEventSynchronize(e1);
+    float ms = 0.f;
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, e0, e1);
+    if (e != cudaSuccess) rc = fail(PARALIA_ERR_CUDA, "link benchmark failed: %s", cudaGetErrorString(e));
+    else *mean_s = ms * 1e-3 / reps;
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+  }
+  PARALiA_free(src, src_loc);
+  PARALiA_free(dst, dst_loc);
+  return rc;
+}
+
+}  // extern "C"

@@ -1,0 +1,414 @@
+// FP64 tile GEMM for sm_100a: C_tile = alpha * sum_parts op(A_p) op(B_p) + beta_c*C_tile
+//                                      (+ beta_src * Csrc).
+//
+// This is the kernel behind every "Dgemm" subkernel; it stands where the reference calls
+// cuBLAS through backend_run_operation (Library_scheduler/src/Subkernel.cpp:168,228) with
+// the parameter block built at Library_scheduler/src/Functions/dgemm.cpp:181-197.
+//
+// Blackwell's tcgen05 tensor path has no FP64 kind, so the FP64 tensor cores are driven
+// with warp-level mma.sync (DMMA). Structure of one CTA (288 threads, one per SM):
+//   * warp 8 is the producer: one lane issues TMA 3-D tiled loads (128-byte swizzle, no
+//     multicast) for a 128 x 16 slice of A and a 16 x 128 slice of B per stage into a
+//     6-stage ring, completion signalled on "full" mbarriers;
+//   * warps 0-7 are consumers: each owns a 64 (m) x 32 (n) piece of the 128 x 128 tile,
+//     reads operand fragments from the swizzled stage with conflict-free 64-bit loads and
+//     issues m16n8k8 DMMA; a warp releases the stage on an "empty" mbarrier;
+//   * the epilogue applies alpha/beta from registers straight to C.
+//
+// Mapping onto the MMA: the instruction computes D[i][j] += sum_k P[i][k] Q[k][j] where a
+// thread ends up holding two j-adjacent values. C is column-major, so j is bound to the
+// GEMM's m (contiguous in memory) and i to n: P fragments come from B, Q fragments from A.
+//
+// k permutation. Inside a 16-deep stage the order in which k values are fed to the MMA is
+// free as long as P and Q agree. Lane t (= lane & 3) of step q (0..3) takes
+//        k(q,t) = 8*(t>>1) + 2*((t+q)&3) + (t&1).
+// With the 128-byte TMA swizzle this choice makes the 16 lanes of a half-warp hit 16
+// different 8-byte bank pairs both when the operand slice is stored k-contiguous
+// ([row][16 k]) and when it is stored row-contiguous ([16-row chunk][k][16 rows]).
+#include "dgemm_tile.cuh"
+#include "sm100_prims.cuh"
+
+namespace paralia {
+using namespace prims;
+
+namespace {
+
+__device__ __forceinline__ void dmma_16x8x8(double (&d)[4], const double (&a)[4], double b0,
+                                            double b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k8.row.col.f64.f64.f64.f64 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};"
+      : "+d"(d[0]), "+d"(d[1]), "+d"(d[2]), "+d"(d[3])
+      : "d"(a[0]), "d"(a[1]), "d"(a[2]), "d"(a[3]), "d"(b0), "d"(b1));
+}
+
+__device__ __forceinline__ int kperm(int q, int t) {
+  return 8 * (t >> 1) + 2 * ((t + q) & 3) + (t & 1);
+}
+
+// Byte offset, inside a 128-row operand slice, of element (row = 16*blk + 8*h + g, k),
+// without the 2048-byte-per-16-rows block term.
+template <bool KC>
+__device__ __forceinline__ uint32_t lane_off(int g, int h, int k) {
+  if (KC) {
+    // [row][16 k]: 128-byte rows, 16-byte chunk index xor (row & 7)
+    return (uint32_t)((h * 8 + g) * 128 + ((((k >> 1) ^ g) & 7) << 4) + ((k & 1) << 3));
+  } else {
+    // [16-row chunk][k][16 rows]: row of the swizzle pattern is k
+    int e = h * 8 + g;
+    return (uint32_t)(k * 128 + ((((e >> 1) ^ (k & 7)) & 7) << 4) + ((e & 1) << 3));
+  }
+}
+
+__device__ __forceinline__ double lds64(const unsigned char* base, uint32_t off) {
+  return *reinterpret_cast<const double*>(base + off);
+}
+
+template <bool A_KC, bool B_KC>
+__global__ void __launch_bounds__(DG_THREADS, 1)
+dgemm_tile_kernel(const __grid_constant__ CUtensorMap mapA,
+                  const __grid_constant__ CUtensorMap mapB,
+                  const __grid_constant__ DgemmArgs args) {
+  extern __shared__ unsigned char smem_raw[];
+  // Swizzled TMA destinations must sit on 1024-byte boundaries.
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + DG_STAGES * DG_STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + DG_STAGES;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + DG_STAGES);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * DG_BM;
+  const int n0 = blockIdx.y * DG_BN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < DG_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], DG_CONSUMER_WARPS);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  if (warp == DG_CONSUMER_WARPS) {
+    // ------------------------------ producer ------------------------------
+    if (lane == 0) {
+      if (args.nparts > 0) {
+        prefetch_tensormap(&mapA);
+        prefetch_tensormap(&mapB);
+      }
+      int it = 0;
+      bool ok = true;
+      for (int p = 0; p < args.nparts && ok; ++p) {
+        const DgemmKPart part = args.parts[p];
+        for (int kk = 0; kk < part.klen; kk += DG_BK, ++it) {
+          const int s = it % DG_STAGES;
+          if (it >= DG_STAGES) {
+            const uint32_t par = (uint32_t)(((it / DG_STAGES) - 1) & 1);
+            if (!mbar_wait_bounded(&empty_bar[s], par, abort_flag)) {
+              if (!*abort_flag) {
+                *abort_flag = 1;
+                atomicExch(args.status, KERR_EMPTY_WAIT_TIMEOUT);
+              }
+              ok = false;
+              break;
+            }
+          }
+          unsigned char* sA = smem + s * DG_STAGE_BYTES;
+          unsigned char* sB = sA + DG_BM * DG_BK * 8;
+          mbar_expect_tx(&full_bar[s], DG_STAGE_BYTES);
+          if (A_KC) {
+            tma_load_3d(sA, &mapA, &full_bar[s], part.a_k + kk, part.a_m + m0, part.a_z);
+          } else {
+#pragma unroll
+            for (int c = 0; c < DG_BM / 16; ++c)
+              tma_load_3d(sA + c * 2048, &mapA, &full_bar[s], part.a_m + m0 + c * 16,
+                          part.a_k + kk, part.a_z);
+          }
+          if (B_KC) {
+            tma_load_3d(sB, &mapB, &full_bar[s], part.b_k + kk, part.b_n + n0, part.b_z);
+          } else {
+#pragma unroll
+            for (int c = 0; c < DG_BN / 16; ++c)
+              tma_load_3d(sB + c * 2048, &mapB, &full_bar[s], part.b_n + n0 + c * 16,
+                          part.b_k + kk, part.b_z);
+          }
+        }
+      }
+      if (!ok || *abort_flag) {
+        // Bailing out: let the copies already issued land before the CTA's shared
+        // memory is released.
+        const int first = it > DG_STAGES ? it - DG_STAGES : 0;
+        for (int j = first; j < it; ++j) {
+          int zero = 0;
+          if (!mbar_wait_bounded(&full_bar[j % DG_STAGES], (uint32_t)((j / DG_STAGES) & 1),
+                                 &zero))
+            atomicExch(args.status, KERR_DRAIN_TIMEOUT);
+        }
+      }
+    }
+    return;
+  }
+
+  // -------------------------------- consumers --------------------------------
+  const int g = lane >> 2;
+  const int t = lane & 3;
+  const int wn = warp & 3;   // 32-column slice of the tile
+  const int wm = warp >> 2;  // 64-row slice of the tile
+
+  // Per-lane byte offsets for the four k steps of a stage and the two 8-row halves.
+  uint32_t offP[4][2], offQ[4][2];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const int k = kperm(q, t);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      offP[q][h] = lane_off<B_KC>(g, h, k) + (uint32_t)(wn * 2 * 2048) +
+                   (uint32_t)(DG_BM * DG_BK * 8);
+      offQ[q][h] = lane_off<A_KC>(g, h, k) + (uint32_t)(wm * 4 * 2048);
+    }
+  }
+
+  double acc[2][8][4];
+#pragma unroll
+  for (int ib = 0; ib < 2; ++ib)
+#pragma unroll
+    for (int jb = 0; jb < 8; ++jb)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) acc[ib][jb][r] = 0.0;
+
+  int total = 0;
+  for (int p = 0; p < args.nparts; ++p) total += (args.parts[p].klen + DG_BK - 1) / DG_BK;
+
+  bool ok = true;
+  for (int it = 0; it < total; ++it) {
+    const int s = it % DG_STAGES;
+    const uint32_t par = (uint32_t)((it / DG_STAGES) & 1);
+    if (!mbar_wait_bounded(&full_bar[s], par, abort_flag)) {
+      if (!*abort_flag) {
+        *abort_flag = 1;
+        atomicExch(args.status, KERR_FULL_WAIT_TIMEOUT);
+      }
+      ok = false;
+      break;
+    }
+    const unsigned char* st = smem + s * DG_STAGE_BYTES;
+#pragma unroll
+    for (int s2 = 0; s2 < 2; ++s2) {
+      double pf[2][4];
+#pragma unroll
+      for (int ib = 0; ib < 2; ++ib) {
+        pf[ib][0] = lds64(st, offP[2 * s2][0] + ib * 2048);
+        pf[ib][1] = lds64(st, offP[2 * s2][1] + ib * 2048);
+        pf[ib][2] = lds64(st, offP[2 * s2 + 1][0] + ib * 2048);
+        pf[ib][3] = lds64(st, offP[2 * s2 + 1][1] + ib * 2048);
+      }
+#pragma unroll
+      for (int jb = 0; jb < 8; ++jb) {
+        const double q0 = lds64(st, offQ[2 * s2][jb & 1] + (jb >> 1) * 2048);
+        const double q1 = lds64(st, offQ[2 * s2 + 1][jb & 1] + (jb >> 1) * 2048);
+        dmma_16x8x8(acc[0][jb], pf[0], q0, q1);
+        dmma_16x8x8(acc[1][jb], pf[1], q0, q1);
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty_bar[s]);
+  }
+  if (!ok) return;
+
+  // -------------------------------- epilogue --------------------------------
+  const double alpha = args.alpha, beta_c = args.beta_c, beta_src = args.beta_src;
+  const bool use_c = beta_c != 0.0;
+  const bool use_src = (args.Csrc != nullptr) && beta_src != 0.0;
+#pragma unroll
+  for (int ib = 0; ib < 2; ++ib) {
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const int n = n0 + wn * 32 + ib * 16 + hh * 8 + g;
+      if (n >= args.N) continue;
+      double* crow = args.C + (int64_t)n * args.ldc;
+      const double* srow = use_src ? args.Csrc + (int64_t)n * args.ldcsrc : nullptr;
+#pragma unroll
+      for (int jb = 0; jb < 8; ++jb) {
+        const int m = m0 + wm * 64 + jb * 8 + 2 * t;
+        if (m >= args.M) continue;
+        double v0 = alpha * acc[ib][jb][2 * hh];
+        double v1 = alpha * acc[ib][jb][2 * hh + 1];
+        if (args.vec_ok && m + 1 < args.M) {
+          if (use_c) {
+            const double2 c = *reinterpret_cast<const double2*>(crow + m);
+            v0 = fma(beta_c, c.x, v0);
+            v1 = fma(beta_c, c.y, v1);
+          }
+          if (use_src) {
+            const double2 c = *reinterpret_cast<const double2*>(srow + m);
+            v0 = fma(beta_src, c.x, v0);
+            v1 = fma(beta_src, c.y, v1);
+          }
+          *reinterpret_cast<double2*>(crow + m) = make_double2(v0, v1);
+        } else {
+          if (use_c) v0 = fma(beta_c, crow[m], v0);
+          if (use_src) v0 = fma(beta_src, srow[m], v0);
+          crow[m] = v0;
+          if (m + 1 < args.M) {
+            if (use_c) v1 = fma(beta_c, crow[m + 1], v1);
+            if (use_src) v1 = fma(beta_src, srow[m + 1], v1);
+            crow[m + 1] = v1;
+          }
+        }
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------
+// Plain-load kernel for operands that TMA cannot address.
+constexpr int GEN_T = 32;
+__global__ void __launch_bounds__(GEN_T* GEN_T)
+dgemm_generic_kernel(int ta, int tb, int M, int N, int K, double alpha, const double* A,
+                     int64_t lda, const double* B, int64_t ldb, double beta, double* C,
+                     int64_t ldc) {
+  __shared__ double sa[GEN_T][GEN_T + 1];
+  __shared__ double sb[GEN_T][GEN_T + 1];
+  const int tx = threadIdx.x % GEN_T, ty = threadIdx.x / GEN_T;
+  const int m = blockIdx.x * GEN_T + tx;
+  const int n = blockIdx.y * GEN_T + ty;
+  double acc = 0.0;
+  for (int k0 = 0; k0 < K; k0 += GEN_T) {
+    {  // sa[kk][mm]
+      const int mm = blockIdx.x * GEN_T + tx, kk = k0 + ty;
+      double v = 0.0;
+      if (mm < M && kk < K) v = ta ? A[(int64_t)mm * lda + kk] : A[(int64_t)kk * lda + mm];
+      sa[ty][tx] = v;
+    }
+    {  // sb[nn][kk]
+      const int kk = k0 + tx, nn = blockIdx.y * GEN_T + ty;
+      double v = 0.0;
+      if (nn < N && kk < K) v = tb ? B[(int64_t)kk * ldb + nn] : B[(int64_t)nn * ldb + kk];
+      sb[ty][tx] = v;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int kk = 0; kk < GEN_T; ++kk) acc = fma(sa[kk][tx], sb[ty][kk], acc);
+    __syncthreads();
+  }
+  if (m < M && n < N) {
+    double v = alpha * acc;
+    if (beta != 0.0) v = fma(beta, C[(int64_t)n * ldc + m], v);
+    C[(int64_t)n * ldc + m] = v;
+  }
+}
+
+// ------------------------------------------------------------------------------
+// Register-only DMMA loops for the calibration database.
+template <int SHAPE>
+__global__ void __launch_bounds__(256) dmma_peak_kernel(int iters, double* sink) {
+  double a[8], b[4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) a[i] = 1.0 + 1e-9 * (threadIdx.x + i);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) b[i] = 1.0 - 1e-9 * (threadIdx.x + i);
+  constexpr int CH = 8;  // independent accumulator chains per warp
+  double d[CH][4];
+#pragma unroll
+  for (int c = 0; c < CH; ++c)
+#pragma unroll
+    for (int r = 0; r < 4; ++r) d[c][r] = 0.0;
+  for (int it = 0; it < iters; ++it) {
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      if (SHAPE == 884) {
+        asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};"
+                     : "+d"(d[c][0]), "+d"(d[c][1])
+                     : "d"(a[c & 7]), "d"(b[c & 3]));
+      } else if (SHAPE == 1684) {
+        asm volatile(
+            "mma.sync.aligned.m16n8k4.row.col.f64.f64.f64.f64 {%0,%1,%2,%3}, {%4,%5}, {%6}, "
+            "{%0,%1,%2,%3};"
+            : "+d"(d[c][0]), "+d"(d[c][1]), "+d"(d[c][2]), "+d"(d[c][3])
+            : "d"(a[0]), "d"(a[1]), "d"(b[c & 3]));
+      } else if (SHAPE == 1688) {
+        asm volatile(
+            "mma.sync.aligned.m16n8k8.row.col.f64.f64.f64.f64 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+            "{%8,%9}, {%0,%1,%2,%3};"
+            : "+d"(d[c][0]), "+d"(d[c][1]), "+d"(d[c][2]), "+d"(d[c][3])
+            : "d"(a[0]), "d"(a[1]), "d"(a[2]), "d"(a[3]), "d"(b[c & 1]), "d"(b[2 + (c & 1)]));
+      } else {
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f64.f64.f64.f64 {%0,%1,%2,%3}, "
+            "{%4,%5,%6,%7,%8,%9,%10,%11}, {%12,%13,%14,%15}, {%0,%1,%2,%3};"
+            : "+d"(d[c][0]), "+d"(d[c][1]), "+d"(d[c][2]), "+d"(d[c][3])
+            : "d"(a[0]), "d"(a[1]), "d"(a[2]), "d"(a[3]), "d"(a[4]), "d"(a[5]), "d"(a[6]),
+              "d"(a[7]), "d"(b[0]), "d"(b[1]), "d"(b[2]), "d"(b[3]));
+      }
+    }
+  }
+  double s = 0.0;
+#pragma unroll
+  for (int c = 0; c < CH; ++c)
+#pragma unroll
+    for (int r = 0; r < 4; ++r) s += d[c][r];
+  if (s == 123.456) sink[0] = s;  // keeps the loop alive without real traffic
+}
+
+}  // namespace
+
+cudaError_t dgemm_tile_configure() {
+  cudaError_t e;
+  e = cudaFuncSetAttribute(dgemm_tile_kernel<false, false>,
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, DG_SMEM_BYTES);
+  if (e != cudaSuccess) return e;
+  e = cudaFuncSetAttribute(dgemm_tile_kernel<false, true>,
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, DG_SMEM_BYTES);
+  if (e != cudaSuccess) return e;
+  e = cudaFuncSetAttribute(dgemm_tile_kernel<true, false>,
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, DG_SMEM_BYTES);
+  if (e != cudaSuccess) return e;
+  e = cudaFuncSetAttribute(dgemm_tile_kernel<true, true>,
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, DG_SMEM_BYTES);
+  return e;
+}
+
+cudaError_t launch_dgemm_tile(const CUtensorMap& mapA, const CUtensorMap& mapB,
+                              const DgemmArgs& args, bool a_kcontig, bool b_kcontig,
+                              cudaStream_t stream) {
+  dim3 grid((args.M + DG_BM - 1) / DG_BM, (args.N + DG_BN - 1) / DG_BN);
+  dim3 block(DG_THREADS);
+  if (a_kcontig) {
+    if (b_kcontig)
+      dgemm_tile_kernel<true, true><<<grid, block, DG_SMEM_BYTES, stream>>>(mapA, mapB, args);
+    else
+      dgemm_tile_kernel<true, false><<<grid, block, DG_SMEM_BYTES, stream>>>(mapA, mapB, args);
+  } else {
+    if (b_kcontig)
+      dgemm_tile_kernel<false, true><<<grid, block, DG_SMEM_BYTES, stream>>>(mapA, mapB, args);
+    else
+      dgemm_tile_kernel<false, false><<<grid, block, DG_SMEM_BYTES, stream>>>(mapA, mapB, args);
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_dgemm_generic(char ta, char tb, int M, int N, int K, double alpha,
+                                 const double* A, int64_t lda, const double* B, int64_t ldb,
+                                 double beta, double* C, int64_t ldc, cudaStream_t stream) {
+  dim3 grid((M + GEN_T - 1) / GEN_T, (N + GEN_T - 1) / GEN_T);
+  dgemm_generic_kernel<<<grid, GEN_T * GEN_T, 0, stream>>>(ta == 'T', tb == 'T', M, N, K, alpha, A,
+                                                           lda, B, ldb, beta, C, ldc);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_dmma_peak(int shape, int iters, int blocks, double* sink,
+                             cudaStream_t stream) {
+  switch (shape) {
+    case 884: dmma_peak_kernel<884><<<blocks, 256, 0, stream>>>(iters, sink); break;
+    case 1684: dmma_peak_kernel<1684><<<blocks, 256, 0, stream>>>(iters, sink); break;
+    case 1688: dmma_peak_kernel<1688><<<blocks, 256, 0, stream>>>(iters, sink); break;
+    case 16816: dmma_peak_kernel<16816><<<blocks, 256, 0, stream>>>(iters, sink); break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace paralia

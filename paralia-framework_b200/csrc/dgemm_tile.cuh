@@ -1,0 +1,60 @@
+// Host-visible description of one launch of the FP64 tile GEMM kernel.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace paralia {
+
+// CTA tile and pipeline shape of the DMMA kernel.
+constexpr int DG_BM = 128;      // rows of C per CTA
+constexpr int DG_BN = 128;      // columns of C per CTA
+constexpr int DG_BK = 16;       // k per pipeline stage (16 doubles = one 128-byte swizzle row)
+constexpr int DG_STAGES = 6;    // 6 x 32 KB of operand tiles in flight
+constexpr int DG_CONSUMER_WARPS = 8;
+constexpr int DG_THREADS = (DG_CONSUMER_WARPS + 1) * 32;  // + one TMA producer warp
+constexpr int DG_STAGE_BYTES = (DG_BM + DG_BN) * DG_BK * 8;
+constexpr int DG_SMEM_BYTES = DG_STAGES * DG_STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int DG_MAX_PARTS = 64;
+
+// One slice of the K loop: where the A and B tiles of that slice start inside the
+// tensors their TMA maps describe. (row, k, z) for A and (k, col, z) for B are logical
+// GEMM coordinates; z selects a block of the tile cache (0 for a user matrix).
+struct DgemmKPart {
+  int32_t a_m, a_k, a_z;
+  int32_t b_k, b_n, b_z;
+  int32_t klen;
+};
+
+struct DgemmArgs {
+  double* C;            // accumulator / output tile, column-major
+  const double* Csrc;   // optional second source added as beta_src*Csrc (may be null)
+  int64_t ldc, ldcsrc;
+  double alpha, beta_c, beta_src;
+  int32_t M, N;         // extent of the C tile
+  int32_t nparts;
+  int32_t vec_ok;       // C and Csrc allow 16-byte accesses
+  int* status;          // device word that receives a KERR_* code on a timed-out wait
+  DgemmKPart parts[DG_MAX_PARTS];
+};
+
+// Launch on `stream`. a_kcontig: A is stored with k contiguous (TransA == 'T' for a
+// column-major A); b_kcontig: B is stored with k contiguous (TransB == 'N').
+cudaError_t launch_dgemm_tile(const CUtensorMap& mapA, const CUtensorMap& mapB,
+                              const DgemmArgs& args, bool a_kcontig, bool b_kcontig,
+                              cudaStream_t stream);
+
+// Plain-load version for operands TMA cannot address (odd leading dimension or a base
+// that is not 16-byte aligned). Same arithmetic, far slower; used only by the direct
+// per-tile entry point.
+cudaError_t launch_dgemm_generic(char ta, char tb, int M, int N, int K, double alpha,
+                                 const double* A, int64_t lda, const double* B, int64_t ldb,
+                                 double beta, double* C, int64_t ldc, cudaStream_t stream);
+
+// Opt the kernels into their dynamic shared memory size; once per device.
+cudaError_t dgemm_tile_configure();
+
+// Register-only DMMA throughput loop. shape in {884, 1684, 1688, 16816}.
+cudaError_t launch_dmma_peak(int shape, int iters, int blocks, double* sink, cudaStream_t stream);
+
+}  // namespace paralia

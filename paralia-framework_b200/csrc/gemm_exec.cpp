@@ -1,0 +1,661 @@
+// Multi-GPU tiled GEMM: static plan, per-GPU tile cache, stream/event overlap engine.
+//
+// This file stands where the reference has PARALiADgemm / PARALiASgemm
+// (Library_scheduler/src/Functions/dgemm.cpp:318-694, sgemm.cpp:296-...) together with
+// the subkernel scheduler underneath them (Library_scheduler/src/Subkernel.cpp:90-247,
+// 384-449). What is kept: square T x T tiles, one subkernel per (mi, ni, ki) with id
+// mi*Nt*Kt + ni*Kt + ki (dgemm.cpp:157-161), every subkernel of a C tile on the GPU that
+// owns the tile (2D block distribution), beta applied lazily after the last k
+// (ALGO_WR_LAZY, dgemm.cpp:173-179,273-279), a tile cached on a peer fetched from the
+// peer instead of the host, C tiles written back as they finish.
+//
+// What is different by design: the order of everything is fixed before the first copy is
+// enqueued (no ETA-driven selection, no rand() tie break, no polling manager thread), so
+// a given problem always runs the same arithmetic in the same order on every GPU.
+// One host thread walks the GPUs round-robin and enqueues, per subkernel, the tile
+// fetches it still needs and its kernel; dependencies are CUDA events only.
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+#include <vector>
+
+#include "autotune.hpp"
+#include "dgemm_tile.cuh"
+#include "runtime.hpp"
+#include "sgemm_tile.cuh"
+#include "exec.hpp"
+
+namespace paralia {
+
+namespace {
+
+inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+inline int64_t round_up(int64_t a, int64_t b) { return ceil_div(a, b) * b; }
+
+struct OperandDesc {
+  const void* ptr = nullptr;
+  int64_t ld = 0;
+  int loc = -1;          // -1 host, >=0 GPU
+  bool trans = false;    // stored transposed w.r.t. its role in the GEMM
+  int64_t rows = 0, cols = 0;  // stored extent
+  bool registered_here = false;
+};
+
+// Where one tile of an operand can be read on one GPU.
+struct Resident {
+  bool present = false;   // fetch enqueued (or native)
+  bool native = false;    // read in place from the user's matrix
+  int block = -1;         // tile-cache block otherwise
+  cudaEvent_t ready = nullptr;
+};
+
+struct UnitState {
+  int dev = -1;
+  std::vector<int> ctiles;             // C tiles (mi*Nt+ni) in processing order
+  std::vector<Resident> a, b, c, csrc; // indexed by tile id of each operand
+  int next_block = 0;
+  int nblocks = 0;
+  CUtensorMap map_slab_kc, map_slab_mn;   // tile cache seen k-contiguous / row-contiguous
+  CUtensorMap map_a_native, map_b_native; // user matrices on this GPU
+  bool a_native_ok = false, b_native_ok = false, c_native = false;
+  size_t cursor = 0;                   // next subkernel (ctile index * Kt + ki) to enqueue
+  std::vector<cudaEvent_t> exec_tail;  // last event per exec stream
+  cudaEvent_t h2d_tail = nullptr, p2p_tail = nullptr;
+};
+
+template <typename T>
+struct GemmCall {
+  char ta, tb;
+  int64_t M, N, K;
+  T alpha, beta;
+  OperandDesc A, B, C;
+  int64_t Tt = 0, TL = 0;   // tile edge, padded edge of a cache block
+  int64_t Mt = 0, Nt = 0, Kt = 0;
+  int exec_streams = 4;
+  bool peer_fetch = true;
+  std::vector<UnitState> units;
+  std::vector<int> ctile_owner;             // C tile -> unit index
+  std::vector<std::vector<int>> a_consumers; // per tile-row mi: units that read A(mi,*)
+  std::vector<std::vector<int>> b_consumers; // per tile-col ni: units that read B(*,ni)
+  paralia_report* rep = nullptr;
+  static constexpr int esz = (int)sizeof(T);
+
+  int64_t mrows(int64_t mi) const { return std::min(Tt, M - mi * Tt); }
+  int64_t ncols(int64_t ni) const { return std::min(Tt, N - ni * Tt); }
+  int64_t klen(int64_t ki) const { return std::min(Tt, K - ki * Tt); }
+  size_t block_bytes() const { return (size_t)TL * TL * esz; }
+  char* block_ptr(const UnitState& u, int blk) const {
+    return static_cast<char*>(Runtime::get().dev(u.dev).slab) + (size_t)blk * block_bytes();
+  }
+};
+
+int norm_trans(char t, bool* out) {
+  switch (t) {
+    case 'N': case 'n': *out = false; return PARALIA_OK;
+    case 'T': case 't': case 'C': case 'c': *out = true; return PARALIA_OK;
+    default: return fail(PARALIA_ERR_INVALID_ARG, "transpose flag '%c' is not N or T", t);
+  }
+}
+
+// Resolve where an operand lives and make host memory DMA-able.
+int resolve_operand(OperandDesc* op, int loc_in, size_t bytes, int ngpu, double* pin_ms) {
+  bool pinned = false;
+  const int actual = pointer_location(op->ptr, &pinned);
+  int loc = loc_in;
+  if (loc == PARALIA_LOC_AUTO) loc = actual;
+  if (loc < -1 || loc >= ngpu)
+    return fail(PARALIA_ERR_INVALID_ARG, "location id %d is neither -1 nor a GPU of this box", loc);
+  if (loc >= 0 && actual != loc)
+    return fail(PARALIA_ERR_INVALID_ARG, "operand declared on GPU %d but the pointer lives on %d",
+                loc, actual);
+  if (loc == -1 && actual >= 0)
+    return fail(PARALIA_ERR_INVALID_ARG, "operand declared on the host but the pointer is on GPU %d",
+                actual);
+  op->loc = loc;
+  if (loc == -1 && !pinned && bytes > 0) {
+    // The reference pins host operands in place for the call (Decom2D::prepareAsync,
+    // dgemm.cpp:413-416) and unpins them at teardown (dgemm.cpp:669-678).
+    const double t0 = wall_ms();
+    cudaError_t e = cudaHostRegister(const_cast<void*>(op->ptr), bytes, cudaHostRegisterPortable);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return fail(PARALIA_ERR_CUDA, "cannot page-lock a host operand of %zu bytes: %s", bytes,
+                  cudaGetErrorString(e));
+    }
+    op->registered_here = true;
+    if (pin_ms) *pin_ms += wall_ms() - t0;
+  }
+  return PARALIA_OK;
+}
+
+void unpin(OperandDesc* op) {
+  if (op->registered_here) {
+    cudaHostUnregister(const_cast<void*>(op->ptr));
+    op->registered_here = false;
+  }
+}
+
+template <typename T>
+struct TileGeom {
+  const char* src;    // first element in the user's matrix
+  int64_t nr, nc;     // stored rows x cols of the tile
+  bool k_is_row;      // k runs along stored rows (contiguous) rather than columns
+};
+
+template <typename T>
+TileGeom<T> geom_a(const GemmCall<T>& g, int64_t mi, int64_t ki) {
+  TileGeom<T> t;
+  if (!g.A.trans) {
+    t.src = (const char*)g.A.ptr + (mi * g.Tt + ki * g.Tt * g.A.ld) * g.esz;
+    t.nr = g.mrows(mi); t.nc = g.klen(ki); t.k_is_row = false;
+  } else {
+    t.src = (const char*)g.A.ptr + (ki * g.Tt + mi * g.Tt * g.A.ld) * g.esz;
+    t.nr = g.klen(ki); t.nc = g.mrows(mi); t.k_is_row = true;
+  }
+  return t;
+}
+template <typename T>
+TileGeom<T> geom_b(const GemmCall<T>& g, int64_t ki, int64_t ni) {
+  TileGeom<T> t;
+  if (!g.B.trans) {
+    t.src = (const char*)g.B.ptr + (ki * g.Tt + ni * g.Tt * g.B.ld) * g.esz;
+    t.nr = g.klen(ki); t.nc = g.ncols(ni); t.k_is_row = true;
+  } else {
+    t.src = (const char*)g.B.ptr + (ni * g.Tt + ki * g.Tt * g.B.ld) * g.esz;
+    t.nr = g.ncols(ni); t.nc = g.klen(ki); t.k_is_row = false;
+  }
+  return t;
+}
+
+template <typename T>
+int take_block(GemmCall<T>& g, UnitState& u, int* blk) {
+  if (u.next_block >= u.nblocks)
+    return fail(PARALIA_ERR_OUT_OF_MEMORY, "GPU %d: tile cache of %d blocks exhausted", u.dev,
+                u.nblocks);
+  *blk = u.next_block++;
+  return PARALIA_OK;
+}
+
+// Zero the k padding of a cache block so that the last 16-deep pipeline stage of an edge
+// tile multiplies zeros, then copy the tile in. `stream` belongs to GPU u.dev.
+template <typename T>
+int copy_tile_in(GemmCall<T>& g, UnitState& u, int blk, const char* src, int64_t src_ld,
+                 const TileGeom<T>& t, cudaStream_t stream, int64_t* byte_counter) {
+  char* dst = g.block_ptr(u, blk);
+  const int64_t kext = t.k_is_row ? t.nr : t.nc;
+  const int64_t kpad = round_up(kext, DG_BK) - kext;
+  if (kpad > 0) {
+    if (t.k_is_row)
+      PL_CUDA(cudaMemset2DAsync(dst + kext * g.esz, g.TL * g.esz, 0, kpad * g.esz, t.nc, stream));
+    else
+      PL_CUDA(cudaMemsetAsync(dst + kext * g.TL * g.esz, 0, kpad * g.TL * g.esz, stream));
+  }
+  PL_CUDA(cudaMemcpy2DAsync(dst, g.TL * g.esz, src, src_ld * g.esz, t.nr * g.esz, t.nc,
+                            cudaMemcpyDefault, stream));
+  if (byte_counter) *byte_counter += t.nr * t.nc * g.esz;
+  return PARALIA_OK;
+}
+
+// Make a tile of A or B readable on unit `ui`; enqueue whatever copies that takes.
+template <typename T>
+int ensure_input(GemmCall<T>& g, int ui, bool is_a, int64_t i0, int64_t i1) {
+  Runtime& rt = Runtime::get();
+  UnitState& u = g.units[ui];
+  const OperandDesc& op = is_a ? g.A : g.B;
+  const int64_t tid = is_a ? i0 * g.Kt + i1 : i0 * g.Nt + i1;
+  Resident& r = is_a ? u.a[tid] : u.b[tid];
+  if (r.present) return PARALIA_OK;
+  const TileGeom<T> t = is_a ? geom_a(g, i0, i1) : geom_b(g, i0, i1);
+  if (op.loc == u.dev && (is_a ? u.a_native_ok : u.b_native_ok)) {
+    r.present = true;
+    r.native = true;
+    return PARALIA_OK;
+  }
+  PL_CUDA(cudaSetDevice(u.dev));
+  PL_TRY(take_block(g, u, &r.block));
+  PL_TRY(rt.get_event(u.dev, &r.ready));
+  DeviceCtx& dc = rt.dev(u.dev);
+  if (op.loc == -1) {
+    // Host-resident tile: one consumer (its "home") pulls it over its host link, the
+    // others take it from the home's cache over NVLink.
+    const std::vector<int>& cons = is_a ? g.a_consumers[i0] : g.b_consumers[i1];
+    int home = ui;
+    if (g.peer_fetch && cons.size() > 1) home = cons[(size_t)(i0 + i1) % cons.size()];
+    if (home != ui && !rt.peer_ok(u.dev, g.units[home].dev)) home = ui;
+    if (home == ui) {
+      PL_TRY(copy_tile_in(g, u, r.block, t.src, op.ld, t, dc.h2d, &g.rep->h2d_bytes));
+      PL_CUDA(cudaEventRecord(r.ready, dc.h2d));
+      u.h2d_tail = r.ready;
+    } else {
+      PL_TRY(ensure_input(g, home, is_a, i0, i1));
+      PL_CUDA(cudaSetDevice(u.dev));
+      UnitState& h = g.units[home];
+      const Resident& hr = is_a ? h.a[tid] : h.b[tid];
+      PL_CUDA(cudaStreamWaitEvent(dc.p2p, hr.ready, 0));
+      // The home's block already carries the zero padding: copy the padded extent.
+      TileGeom<T> tp = t;
+      if (t.k_is_row) tp.nr = round_up(t.nr, DG_BK); else tp.nc = round_up(t.nc, DG_BK);
+      PL_CUDA(cudaMemcpy2DAsync(g.block_ptr(u, r.block), g.TL * g.esz, g.block_ptr(h, hr.block),
+                                g.TL * g.esz, tp.nr * g.esz, tp.nc, cudaMemcpyDefault, dc.p2p));
+      g.rep->p2p_bytes += t.nr * t.nc * g.esz;
+      PL_CUDA(cudaEventRecord(r.ready, dc.p2p));
+      u.p2p_tail = r.ready;
+    }
+  } else {
+    // Operand lives on a GPU (another one, or this one at an address TMA cannot use).
+    PL_TRY(copy_tile_in(g, u, r.block, t.src, op.ld, t, dc.p2p,
+                        op.loc == u.dev ? &g.rep->d2d_bytes : &g.rep->p2p_bytes));
+    PL_CUDA(cudaEventRecord(r.ready, dc.p2p));
+    u.p2p_tail = r.ready;
+  }
+  r.present = true;
+  return PARALIA_OK;
+}
+
+template <typename T>
+int launch_tile(const CUtensorMap& mapA, const CUtensorMap& mapB, const DgemmArgs& args,
+                bool a_kc, bool b_kc, cudaStream_t s);
+
+template <>
+int launch_tile<double>(const CUtensorMap& mapA, const CUtensorMap& mapB, const DgemmArgs& args,
+                        bool a_kc, bool b_kc, cudaStream_t s) {
+  PL_CUDA(launch_dgemm_tile(mapA, mapB, args, a_kc, b_kc, s));
+  return PARALIA_OK;
+}
+
+// Enqueue subkernels [ki0, ki1) of C tile `ct` on unit ui as one launch.
+template <typename T>
+int enqueue_subkernels(GemmCall<T>& g, int ui, int order_idx, int ct, int ki0, int ki1);
+
+template <>
+int enqueue_subkernels<double>(GemmCall<double>& g, int ui, int order_idx, int ct, int ki0,
+                               int ki1) {
+  Runtime& rt = Runtime::get();
+  UnitState& u = g.units[ui];
+  DeviceCtx& dc = rt.dev(u.dev);
+  const int64_t mi = ct / g.Nt, ni = ct % g.Nt;
+  const int sidx = order_idx % g.exec_streams;
+  cudaStream_t es = dc.exec[sidx];
+  PL_CUDA(cudaSetDevice(u.dev));
+
+  DgemmArgs args;
+  memset(&args, 0, sizeof(args));
+  args.nparts = 0;
+  bool a_native = false, b_native = false;
+  for (int ki = ki0; ki < ki1; ++ki) {
+    PL_TRY(ensure_input(g, ui, true, mi, ki));
+    PL_TRY(ensure_input(g, ui, false, ki, ni));
+    PL_CUDA(cudaSetDevice(u.dev));
+    const Resident& ra = u.a[mi * g.Kt + ki];
+    const Resident& rb = u.b[ki * g.Nt + ni];
+    DgemmKPart& p = args.parts[args.nparts++];
+    p.klen = (int32_t)g.klen(ki);
+    a_native = ra.native;
+    b_native = rb.native;
+    if (ra.native) { p.a_m = (int32_t)(mi * g.Tt); p.a_k = (int32_t)(ki * g.Tt); p.a_z = 0; }
+    else { p.a_m = 0; p.a_k = 0; p.a_z = ra.block; PL_CUDA(cudaStreamWaitEvent(es, ra.ready, 0)); }
+    if (rb.native) { p.b_k = (int32_t)(ki * g.Tt); p.b_n = (int32_t)(ni * g.Tt); p.b_z = 0; }
+    else { p.b_k = 0; p.b_n = 0; p.b_z = rb.block; PL_CUDA(cudaStreamWaitEvent(es, rb.ready, 0)); }
+  }
+
+  const bool first = (ki0 == 0), last = (ki1 == g.Kt);
+  Resident& rc = u.c[ct];
+  if (!rc.present) {
+    rc.present = true;
+    if (u.c_native) rc.native = true;
+    else PL_TRY(take_block(g, u, &rc.block));
+  }
+  args.M = (int32_t)g.mrows(mi);
+  args.N = (int32_t)g.ncols(ni);
+  args.alpha = g.alpha;
+  args.status = dc.status_dev;
+  args.Csrc = nullptr;
+  args.beta_src = 0.0;
+  if (rc.native) {
+    // C lives on this GPU: update it in place, beta on the first k only
+    // (the reference switches such tiles to plain WR, dgemm.cpp:262-263).
+    args.C = (double*)g.C.ptr + mi * g.Tt + ni * g.Tt * g.C.ld;
+    args.ldc = g.C.ld;
+    args.beta_c = first ? g.beta : 1.0;
+    args.vec_ok = tma_addressable(g.C.ptr, g.C.ld, g.esz) ? 1 : 0;
+  } else {
+    args.C = (double*)g.block_ptr(u, rc.block);
+    args.ldc = g.TL;
+    args.beta_c = first ? 0.0 : 1.0;   // WR_LAZY: accumulate from zero (dgemm.cpp:273-279)
+    args.vec_ok = 1;
+    if (g.beta != 0.0) {
+      Resident& rs = u.csrc[ct];
+      if (first && !rs.present) {
+        // Original C tile, needed only by the last k: fetched behind the first k's inputs.
+        PL_TRY(take_block(g, u, &rs.block));
+        PL_TRY(rt.get_event(u.dev, &rs.ready));
+        TileGeom<double> t;
+        t.src = (const char*)g.C.ptr + (mi * g.Tt + ni * g.Tt * g.C.ld) * g.esz;
+        t.nr = args.M; t.nc = args.N; t.k_is_row = false;
+        cudaStream_t cs = g.C.loc == -1 ? dc.h2d : dc.p2p;
+        PL_CUDA(cudaMemcpy2DAsync(g.block_ptr(u, rs.block), g.TL * g.esz, t.src, g.C.ld * g.esz,
+                                  t.nr * g.esz, t.nc, cudaMemcpyDefault, cs));
+        if (g.C.loc == -1) g.rep->h2d_bytes += t.nr * t.nc * g.esz;
+        else g.rep->p2p_bytes += t.nr * t.nc * g.esz;
+        PL_CUDA(cudaEventRecord(rs.ready, cs));
+        if (g.C.loc == -1) u.h2d_tail = rs.ready; else u.p2p_tail = rs.ready;
+        rs.present = true;
+      }
+      if (last) {
+        PL_CUDA(cudaStreamWaitEvent(es, rs.ready, 0));
+        args.Csrc = (const double*)g.block_ptr(u, rs.block);
+        args.ldcsrc = g.TL;
+        args.beta_src = g.beta;
+      }
+    }
+  }
+  const bool a_kc = g.A.trans, b_kc = !g.B.trans;
+  const CUtensorMap& mapA = a_native ? u.map_a_native : (a_kc ? u.map_slab_kc : u.map_slab_mn);
+  const CUtensorMap& mapB = b_native ? u.map_b_native : (b_kc ? u.map_slab_kc : u.map_slab_mn);
+  PL_TRY(launch_tile<double>(mapA, mapB, args, a_kc, b_kc, es));
+  g.rep->kernel_launches += 1;
+
+  cudaEvent_t done;
+  PL_TRY(rt.get_event(u.dev, &done));
+  PL_CUDA(cudaEventRecord(done, es));
+  u.exec_tail[sidx] = done;
+  if (last && !rc.native) {
+    // Write the finished tile back to where C lives (reference: WBTileMap, dgemm.cpp:583).
+    PL_CUDA(cudaStreamWaitEvent(dc.d2h, done, 0));
+    char* dst = (char*)g.C.ptr + (mi * g.Tt + ni * g.Tt * g.C.ld) * g.esz;
+    PL_CUDA(cudaMemcpy2DAsync(dst, g.C.ld * g.esz, g.block_ptr(u, rc.block), g.TL * g.esz,
+                              (size_t)args.M * g.esz, args.N, cudaMemcpyDefault, dc.d2h));
+    if (g.C.loc == -1) g.rep->d2h_bytes += (int64_t)args.M * args.N * g.esz;
+    else g.rep->p2p_bytes += (int64_t)args.M * args.N * g.esz;
+  }
+  return PARALIA_OK;
+}
+
+// How many consecutive k of one C tile go into one launch. Operands already on the GPU
+// can run a whole k chain at once (the accumulator stays in registers); streamed tiles
+// start with single-k launches so compute begins as soon as the first pair has landed,
+// and switch to longer chains once the fetch stream is ahead.
+template <typename T>
+int kchain_len(const GemmCall<T>& g, const UnitState& u, int order_idx) {
+  static const int forced = [] {
+    const char* e = getenv("PARALIA_KCHAIN");
+    return e ? atoi(e) : 0;
+  }();
+  int len;
+  if (forced > 0) len = forced;
+  else {
+    const bool a_here = (g.A.loc == u.dev && u.a_native_ok);
+    const bool b_here = (g.B.loc == u.dev && u.b_native_ok);
+    if (a_here && b_here) len = (int)g.Kt;
+    else if (order_idx < g.exec_streams) len = 1;
+    else len = 4;
+  }
+  len = std::min<int>(len, DG_MAX_PARTS);
+  return std::max(len, 1);
+}
+
+template <typename T>
+int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha, const T* A,
+             int64_t ldA, int locA, const T* B, int64_t ldB, int locB, T beta, T* C, int64_t ldC,
+             int locC, const paralia_ctl* ctl, paralia_report* out, const char* func) {
+  const double t_call0 = wall_ms();
+  paralia_report local_rep;
+  paralia_report* rep = out ? out : &local_rep;
+  memset(rep, 0, sizeof(*rep));
+
+  GemmCall<T> g;
+  g.rep = rep;
+  PL_TRY(norm_trans(TransA, &g.A.trans));
+  PL_TRY(norm_trans(TransB, &g.B.trans));
+  g.ta = g.A.trans ? 'T' : 'N';
+  g.tb = g.B.trans ? 'T' : 'N';
+  if (M < 0 || N < 0 || K < 0) return fail(PARALIA_ERR_INVALID_ARG, "negative dimension");
+  g.M = M; g.N = N; g.K = K; g.alpha = alpha; g.beta = beta;
+  g.A.ptr = A; g.A.ld = ldA; g.A.rows = g.A.trans ? K : M; g.A.cols = g.A.trans ? M : K;
+  g.B.ptr = B; g.B.ld = ldB; g.B.rows = g.B.trans ? N : K; g.B.cols = g.B.trans ? K : N;
+  g.C.ptr = C; g.C.ld = ldC; g.C.rows = M; g.C.cols = N;
+  if (ldA < std::max<int64_t>(1, g.A.rows) || ldB < std::max<int64_t>(1, g.B.rows) ||
+      ldC < std::max<int64_t>(1, M))
+    return fail(PARALIA_ERR_INVALID_ARG, "leading dimension smaller than the stored row count");
+  if (M == 0 || N == 0) return PARALIA_OK;
+  if ((!A && K > 0) || (!B && K > 0) || !C) return fail(PARALIA_ERR_INVALID_ARG, "NULL operand");
+  if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX)
+    return fail(PARALIA_ERR_INVALID_ARG, "dimension exceeds 2^31-1");
+
+  Runtime& rt = Runtime::get();
+  PL_TRY(rt.init());
+  std::lock_guard<std::mutex> call_lock(rt.call_mutex());
+  DeviceGuard dev_guard;
+  const int ngpu = rt.device_count();
+
+  double pin_ms = 0.0;
+  int rc = PARALIA_OK;
+  if (K > 0) {
+    rc = resolve_operand(&g.A, locA, (size_t)g.A.ld * g.A.cols * g.esz, ngpu, &pin_ms);
+    if (rc == PARALIA_OK)
+      rc = resolve_operand(&g.B, locB, (size_t)g.B.ld * g.B.cols * g.esz, ngpu, &pin_ms);
+  } else {
+    g.A.loc = g.B.loc = -1;
+  }
+  if (rc == PARALIA_OK) rc = resolve_operand(&g.C, locC, (size_t)g.C.ld * N * g.esz, ngpu, &pin_ms);
+  const bool keep_pinned = ctl && (ctl->flags & PARALIA_FLAG_KEEP_PINNED);
+  auto cleanup_pins = [&]() {
+    if (!keep_pinned) { unpin(&g.A); unpin(&g.B); unpin(&g.C); }
+  };
+  if (rc != PARALIA_OK) { cleanup_pins(); return rc; }
+  rep->pin_ms = pin_ms;
+
+  // ------------------------------ plan ------------------------------
+  const double t_plan0 = wall_ms();
+  GemmModelInput mi_in;
+  mi_in.esz = g.esz; mi_in.ta = g.ta; mi_in.tb = g.tb;
+  mi_in.M = M; mi_in.N = N; mi_in.K = std::max<int64_t>(K, 1);
+  mi_in.locA = g.A.loc; mi_in.locB = g.B.loc; mi_in.locC = g.C.loc;
+  mi_in.beta_nonzero = beta != (T)0;
+  mi_in.func = func;
+  paralia_ctl eff_ctl;
+  memset(&eff_ctl, 0, sizeof(eff_ctl));
+  if (ctl) eff_ctl = *ctl;
+  if (eff_ctl.T > 0) {
+    // Tiles that are not the whole problem must be a multiple of the 16-deep pipeline stage.
+    const int64_t maxdim = std::max(M, std::max(N, mi_in.K));
+    if (eff_ctl.T < maxdim && (eff_ctl.T % DG_BK)) eff_ctl.T = std::max<int64_t>(DG_BK, eff_ctl.T - eff_ctl.T % DG_BK);
+  }
+  paralia_report tuned;
+  rc = autotune_gemm(mi_in, ngpu, &eff_ctl, &tuned);
+  if (rc != PARALIA_OK) { cleanup_pins(); return rc; }
+  g.Tt = tuned.T;
+  if (g.Tt % DG_BK && g.Tt < std::max(M, std::max(N, mi_in.K)))
+    g.Tt = std::max<int64_t>(DG_BK, g.Tt - g.Tt % DG_BK);
+  g.TL = round_up(g.Tt, DG_BK);
+  g.Mt = ceil_div(M, g.Tt); g.Nt = ceil_div(N, g.Tt); g.Kt = K > 0 ? ceil_div(K, g.Tt) : 0;
+  g.exec_streams = eff_ctl.exec_streams > 0 ? std::min(eff_ctl.exec_streams, MAX_EXEC_STREAMS) : 4;
+  g.peer_fetch = !(eff_ctl.flags & PARALIA_FLAG_NO_PEER_FETCH);
+
+  std::vector<std::vector<int>> lists;
+  int d1 = 1, d2 = 1;
+  const int kt_for_ids = (int)std::max<int64_t>(g.Kt, 1);
+  int active = distribute_subkernels_2d(tuned.active_unit_num, (int)g.Mt, (int)g.Nt, kt_for_ids,
+                                        &lists, &d1, &d2);
+  if (active <= 0) { cleanup_pins(); return fail(PARALIA_ERR_INVALID_ARG, "subkernel distribution failed"); }
+  *rep = tuned;
+  rep->T = g.Tt;
+  rep->active_unit_num = active;
+  rep->grid_d1 = d1; rep->grid_d2 = d2;
+  rep->subkernel_num = g.Mt * g.Nt * kt_for_ids;
+  rep->pin_ms = pin_ms;
+
+  g.units.assign(active, UnitState());
+  g.ctile_owner.assign(g.Mt * g.Nt, -1);
+  g.a_consumers.assign(g.Mt, std::vector<int>());
+  g.b_consumers.assign(g.Nt, std::vector<int>());
+  for (int ui = 0; ui < active; ++ui) {
+    UnitState& u = g.units[ui];
+    u.dev = tuned.active_unit_id_list[ui];
+    rep->subkernels_per_unit[ui] = (int)lists[ui].size();
+    rep->active_unit_score[ui] = 1.0 / active;
+    for (int sk : lists[ui]) {
+      const int ct = sk / kt_for_ids;
+      if (g.ctile_owner[ct] == -1) {
+        g.ctile_owner[ct] = ui;
+        u.ctiles.push_back(ct);
+      } else if (g.ctile_owner[ct] != ui) {
+        cleanup_pins();
+        return fail(PARALIA_ERR_UNSUPPORTED, "distribution split one C tile across units");
+      }
+    }
+  }
+  for (int64_t ct = 0; ct < g.Mt * g.Nt; ++ct) {
+    const int ui = g.ctile_owner[ct];
+    auto add = [](std::vector<int>& v, int x) {
+      if (std::find(v.begin(), v.end(), x) == v.end()) v.push_back(x);
+    };
+    add(g.a_consumers[ct / g.Nt], ui);
+    add(g.b_consumers[ct % g.Nt], ui);
+  }
+
+  // ------------------------------ resources ------------------------------
+  double alloc_ms = 0.0;
+  auto fail_out = [&](int code) { cleanup_pins(); return code; };
+  for (int ui = 0; ui < active; ++ui) {
+    UnitState& u = g.units[ui];
+    rc = rt.ensure_device(u.dev);
+    if (rc != PARALIA_OK) return fail_out(rc);
+    rt.release_events(u.dev);
+    u.a.assign(g.Mt * std::max<int64_t>(g.Kt, 1), Resident());
+    u.b.assign(std::max<int64_t>(g.Kt, 1) * g.Nt, Resident());
+    u.c.assign(g.Mt * g.Nt, Resident());
+    u.csrc.assign(g.Mt * g.Nt, Resident());
+    u.exec_tail.assign(g.exec_streams, nullptr);
+    u.a_native_ok = g.A.loc == u.dev && tma_addressable(g.A.ptr, g.A.ld, g.esz);
+    u.b_native_ok = g.B.loc == u.dev && tma_addressable(g.B.ptr, g.B.ld, g.esz);
+    u.c_native = g.C.loc == u.dev;
+    // Blocks this unit needs if nothing is ever evicted: the A tile rows and B tile
+    // columns of its C tiles, plus accumulator (and original-C) blocks
+    // (reference sizing: 1 + At + Bt + 2*Ct, dgemm.cpp:80-87).
+    std::vector<char> rows(g.Mt, 0), cols(g.Nt, 0);
+    for (int ct : u.ctiles) { rows[ct / g.Nt] = 1; cols[ct % g.Nt] = 1; }
+    int64_t need = 0;
+    if (!u.a_native_ok) for (int64_t r = 0; r < g.Mt; ++r) if (rows[r]) need += g.Kt;
+    if (!u.b_native_ok) for (int64_t c = 0; c < g.Nt; ++c) if (cols[c]) need += g.Kt;
+    // A home GPU may also hold tiles it forwards but never reads: bounded by one extra
+    // panel per operand; count what the home rule can send here.
+    if (g.peer_fetch && active > 1) {
+      if (g.A.loc == -1) need += 0;  // homes are always consumers of the tile row
+      if (g.B.loc == -1) need += 0;
+    }
+    if (!u.c_native) need += (int64_t)u.ctiles.size() * ((beta != (T)0) ? 2 : 1);
+    u.nblocks = (int)need;
+    size_t bytes = (size_t)need * g.block_bytes();
+    if (eff_ctl.cache_limit > 0 && bytes > (size_t)eff_ctl.cache_limit)
+      return fail_out(fail(PARALIA_ERR_OUT_OF_MEMORY,
+                           "GPU %d needs %zu bytes of tile cache but cache_limit is %lld", u.dev,
+                           bytes, (long long)eff_ctl.cache_limit));
+    if (bytes > 0) {
+      rc = rt.ensure_slab(u.dev, bytes, &alloc_ms);
+      if (rc != PARALIA_OK) return fail_out(rc);
+      DeviceCtx& dc = rt.dev(u.dev);
+      const uint64_t nb = dc.slab_bytes / g.block_bytes();
+      rc = make_tensor_map(&u.map_slab_kc, dc.slab, g.esz, g.TL, g.TL, nb, g.TL * g.esz,
+                           g.block_bytes(), 16, 128);
+      if (rc == PARALIA_OK)
+        rc = make_tensor_map(&u.map_slab_mn, dc.slab, g.esz, g.TL, g.TL, nb, g.TL * g.esz,
+                             g.block_bytes(), 16, 16);
+      if (rc != PARALIA_OK) return fail_out(rc);
+    }
+    if (u.a_native_ok && K > 0) {
+      rc = make_tensor_map(&u.map_a_native, g.A.ptr, g.esz, g.A.rows, g.A.cols, 1, g.A.ld * g.esz,
+                           (uint64_t)g.A.ld * g.A.cols * g.esz, 16, g.A.trans ? 128 : 16);
+      if (rc != PARALIA_OK) return fail_out(rc);
+    }
+    if (u.b_native_ok && K > 0) {
+      rc = make_tensor_map(&u.map_b_native, g.B.ptr, g.esz, g.B.rows, g.B.cols, 1, g.B.ld * g.esz,
+                           (uint64_t)g.B.ld * g.B.cols * g.esz, 16, g.B.trans ? 16 : 128);
+      if (rc != PARALIA_OK) return fail_out(rc);
+    }
+  }
+  rep->alloc_ms = alloc_ms;
+  rep->plan_ms = wall_ms() - t_plan0 - alloc_ms;
+
+  // ------------------------------ enqueue ------------------------------
+  for (int ui = 0; ui < active; ++ui) {
+    UnitState& u = g.units[ui];
+    DeviceCtx& dc = rt.dev(u.dev);
+    if (cudaSetDevice(u.dev) != cudaSuccess || cudaEventRecord(dc.t_begin, dc.h2d) != cudaSuccess)
+      return fail_out(fail(PARALIA_ERR_CUDA, "cannot record the start event on GPU %d", u.dev));
+    // Nothing of this call may start before the start event.
+    for (int s = 0; s < g.exec_streams; ++s) cudaStreamWaitEvent(dc.exec[s], dc.t_begin, 0);
+    cudaStreamWaitEvent(dc.p2p, dc.t_begin, 0);
+    cudaStreamWaitEvent(dc.d2h, dc.t_begin, 0);
+  }
+  // Round-robin over the GPUs, one launch per turn (the reference's fire loop walks the
+  // devices the same way, dgemm.cpp:516-544).
+  const int kt_loop = (int)std::max<int64_t>(g.Kt, 1);
+  bool work_left = true;
+  while (work_left) {
+    work_left = false;
+    for (int ui = 0; ui < active; ++ui) {
+      UnitState& u = g.units[ui];
+      const size_t total = u.ctiles.size() * (size_t)kt_loop;
+      if (u.cursor >= total) continue;
+      const int order_idx = (int)(u.cursor / kt_loop);
+      const int ki0 = (int)(u.cursor % kt_loop);
+      int ki1 = g.Kt == 0 ? 0 : std::min<int>(kt_loop, ki0 + kchain_len(g, u, order_idx));
+      if (g.Kt == 0) {
+        rc = enqueue_subkernels<T>(g, ui, order_idx, u.ctiles[order_idx], 0, 0);
+        u.cursor = (size_t)(order_idx + 1) * kt_loop;
+      } else {
+        rc = enqueue_subkernels<T>(g, ui, order_idx, u.ctiles[order_idx], ki0, ki1);
+        u.cursor += (size_t)(ki1 - ki0);
+      }
+      if (rc != PARALIA_OK) break;
+      if (u.cursor < total) work_left = true;
+    }
+    if (rc != PARALIA_OK) break;
+  }
+  // ------------------------------ join ------------------------------
+  double dev_ms = 0.0;
+  for (int ui = 0; ui < active; ++ui) {
+    UnitState& u = g.units[ui];
+    DeviceCtx& dc = rt.dev(u.dev);
+    cudaSetDevice(u.dev);
+    if (rc == PARALIA_OK) {
+      for (int s = 0; s < g.exec_streams; ++s)
+        if (u.exec_tail[s]) cudaStreamWaitEvent(dc.d2h, u.exec_tail[s], 0);
+      if (u.h2d_tail) cudaStreamWaitEvent(dc.d2h, u.h2d_tail, 0);
+      if (u.p2p_tail) cudaStreamWaitEvent(dc.d2h, u.p2p_tail, 0);
+      cudaEventRecord(dc.t_end, dc.d2h);
+    }
+  }
+  for (int ui = 0; ui < active; ++ui) {
+    UnitState& u = g.units[ui];
+    DeviceCtx& dc = rt.dev(u.dev);
+    cudaSetDevice(u.dev);
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess && rc == PARALIA_OK)
+      rc = fail(PARALIA_ERR_CUDA, "GPU %d failed while running the plan: %s", u.dev,
+                cudaGetErrorString(e));
+    if (rc == PARALIA_OK) {
+      float ms = 0.f;
+      if (cudaEventElapsedTime(&ms, dc.t_begin, dc.t_end) == cudaSuccess)
+        dev_ms = std::max(dev_ms, (double)ms);
+    }
+  }
+  if (rc == PARALIA_OK)
+    for (int ui = 0; ui < active && rc == PARALIA_OK; ++ui) rc = rt.check_status(g.units[ui].dev);
+  cleanup_pins();
+  rep->device_ms = dev_ms;
+  rep->host_ms = wall_ms() - t_call0;
+  return rc;
+}
+
+}  // namespace
+
+int exec_dgemm(char ta, char tb, int64_t M, int64_t N, int64_t K, double alpha, const double* A,
+               int64_t ldA, int locA, const double* B, int64_t ldB, int locB, double beta,
+               double* C, int64_t ldC, int locC, const paralia_ctl* ctl, paralia_report* out) {
+  return run_gemm<double>(ta, tb, M, N, K, alpha, A, ldA, locA, B, ldB, locB, beta, C, ldC, locC,
+                          ctl, out, "Dgemm");
+}
+
+}  // namespace paralia

@@ -1,0 +1,264 @@
+#include "runtime.hpp"
+
+#include <chrono>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "dgemm_tile.cuh"
+#include "sgemm_tile.cuh"
+
+namespace paralia {
+
+static thread_local char g_err[1024] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+const char* last_error_cstr() { return g_err; }
+
+double wall_ms() {
+  using namespace std::chrono;
+  return duration<double, std::milli>(steady_clock::now().time_since_epoch()).count();
+}
+
+Runtime& Runtime::get() {
+  static Runtime rt;
+  return rt;
+}
+
+int Runtime::init() {
+  std::lock_guard<std::mutex> lk(init_mutex_);
+  if (inited_) return PARALIA_OK;
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess || n <= 0) {
+    cudaGetLastError();
+    return fail(PARALIA_ERR_NO_DEVICE, "no CUDA device visible (%s)",
+                e == cudaSuccess ? "count is 0" : cudaGetErrorString(e));
+  }
+  if (n > PARALIA_MAX_UNITS) n = PARALIA_MAX_UNITS;
+  DeviceGuard guard;
+  ndev_ = n;
+  devs_.assign(n, DeviceCtx());
+  for (int d = 0; d < n; ++d) devs_[d].dev = d;
+  // Peer access between every pair (reference: CoCoEnableLinks for every location,
+  // dgemm.cpp:423). On an NVSwitch box every pair is reachable at the same bandwidth.
+  for (int a = 0; a < n; ++a) {
+    PL_CUDA(cudaSetDevice(a));
+    for (int b = 0; b < n; ++b) {
+      if (a == b) continue;
+      int can = 0;
+      PL_CUDA(cudaDeviceCanAccessPeer(&can, a, b));
+      if (can) {
+        cudaError_t pe = cudaDeviceEnablePeerAccess(b, 0);
+        if (pe == cudaErrorPeerAccessAlreadyEnabled) {
+          cudaGetLastError();
+          pe = cudaSuccess;
+        }
+        peer_[a][b] = (pe == cudaSuccess);
+        if (pe != cudaSuccess) cudaGetLastError();
+      }
+    }
+  }
+  inited_ = true;
+  return PARALIA_OK;
+}
+
+int Runtime::ensure_device(int d) {
+  if (d < 0 || d >= ndev_) return fail(PARALIA_ERR_INVALID_ARG, "GPU id %d out of range", d);
+  DeviceCtx& c = devs_[d];
+  if (c.ready) return PARALIA_OK;
+  PL_CUDA(cudaSetDevice(d));
+  PL_CUDA(cudaStreamCreateWithFlags(&c.h2d, cudaStreamNonBlocking));
+  PL_CUDA(cudaStreamCreateWithFlags(&c.d2h, cudaStreamNonBlocking));
+  PL_CUDA(cudaStreamCreateWithFlags(&c.p2p, cudaStreamNonBlocking));
+  for (int i = 0; i < MAX_EXEC_STREAMS; ++i)
+    PL_CUDA(cudaStreamCreateWithFlags(&c.exec[i], cudaStreamNonBlocking));
+  PL_CUDA(cudaEventCreate(&c.t_begin));
+  PL_CUDA(cudaEventCreate(&c.t_end));
+  PL_CUDA(cudaMalloc(&c.status_dev, sizeof(int)));
+  PL_CUDA(cudaMemset(c.status_dev, 0, sizeof(int)));
+  PL_CUDA(dgemm_tile_configure());
+  PL_CUDA(sgemm_tile_configure());
+  c.ready = true;
+  return PARALIA_OK;
+}
+
+int Runtime::ensure_slab(int d, size_t bytes, double* alloc_ms) {
+  DeviceCtx& c = devs_[d];
+  if (c.slab_bytes >= bytes) return PARALIA_OK;
+  const double t0 = wall_ms();
+  PL_CUDA(cudaSetDevice(d));
+  if (c.slab) {
+    PL_CUDA(cudaDeviceSynchronize());
+    PL_CUDA(cudaFree(c.slab));
+    c.slab = nullptr;
+    c.slab_bytes = 0;
+  }
+  cudaError_t e = cudaMalloc(&c.slab, bytes);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    c.slab = nullptr;
+    return fail(PARALIA_ERR_OUT_OF_MEMORY, "GPU %d: cannot allocate a %zu-byte tile cache (%s)", d,
+                bytes, cudaGetErrorString(e));
+  }
+  c.slab_bytes = bytes;
+  if (alloc_ms) *alloc_ms += wall_ms() - t0;
+  return PARALIA_OK;
+}
+
+int Runtime::free_slab(int d) {
+  if (d < 0 || d >= ndev_) return fail(PARALIA_ERR_INVALID_ARG, "GPU id %d out of range", d);
+  DeviceCtx& c = devs_[d];
+  if (!c.slab) return PARALIA_OK;
+  PL_CUDA(cudaSetDevice(d));
+  PL_CUDA(cudaDeviceSynchronize());
+  PL_CUDA(cudaFree(c.slab));
+  c.slab = nullptr;
+  c.slab_bytes = 0;
+  return PARALIA_OK;
+}
+
+int Runtime::ensure_dot_scratch(int d, size_t partials_n, size_t results_n) {
+  DeviceCtx& c = devs_[d];
+  PL_CUDA(cudaSetDevice(d));
+  if (c.dot_partials_n < partials_n) {
+    if (c.dot_partials) PL_CUDA(cudaFree(c.dot_partials));
+    PL_CUDA(cudaMalloc(&c.dot_partials, partials_n * sizeof(double)));
+    c.dot_partials_n = partials_n;
+  }
+  if (c.dot_results_n < results_n) {
+    if (c.dot_results) PL_CUDA(cudaFree(c.dot_results));
+    if (c.dot_results_host) PL_CUDA(cudaFreeHost(c.dot_results_host));
+    PL_CUDA(cudaMalloc(&c.dot_results, results_n * sizeof(double)));
+    PL_CUDA(cudaMallocHost(&c.dot_results_host, results_n * sizeof(double)));
+    c.dot_results_n = results_n;
+  }
+  return PARALIA_OK;
+}
+
+int Runtime::get_event(int d, cudaEvent_t* ev) {
+  DeviceCtx& c = devs_[d];
+  if (c.events_used == c.event_pool.size()) {
+    PL_CUDA(cudaSetDevice(d));
+    cudaEvent_t e;
+    PL_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    c.event_pool.push_back(e);
+  }
+  *ev = c.event_pool[c.events_used++];
+  return PARALIA_OK;
+}
+
+int Runtime::check_status(int d) {
+  DeviceCtx& c = devs_[d];
+  if (!c.ready) return PARALIA_OK;
+  int word = 0;
+  PL_CUDA(cudaSetDevice(d));
+  PL_CUDA(cudaMemcpy(&word, c.status_dev, sizeof(int), cudaMemcpyDeviceToHost));
+  if (word != 0) {
+    PL_CUDA(cudaMemset(c.status_dev, 0, sizeof(int)));
+    return fail(PARALIA_ERR_TIMEOUT, "GPU %d: a kernel gave up on a bounded wait (code %d)", d,
+                word);
+  }
+  return PARALIA_OK;
+}
+
+int Runtime::finalize() {
+  std::lock_guard<std::mutex> lk(init_mutex_);
+  if (!inited_) return PARALIA_OK;
+  DeviceGuard guard;
+  for (int d = 0; d < ndev_; ++d) {
+    DeviceCtx& c = devs_[d];
+    if (cudaSetDevice(d) != cudaSuccess) continue;
+    cudaDeviceSynchronize();
+    if (c.slab) cudaFree(c.slab);
+    if (c.status_dev) cudaFree(c.status_dev);
+    if (c.dot_partials) cudaFree(c.dot_partials);
+    if (c.dot_results) cudaFree(c.dot_results);
+    if (c.dot_results_host) cudaFreeHost(c.dot_results_host);
+    for (cudaEvent_t e : c.event_pool) cudaEventDestroy(e);
+    if (c.ready) {
+      cudaStreamDestroy(c.h2d);
+      cudaStreamDestroy(c.d2h);
+      cudaStreamDestroy(c.p2p);
+      for (int i = 0; i < MAX_EXEC_STREAMS; ++i) cudaStreamDestroy(c.exec[i]);
+      cudaEventDestroy(c.t_begin);
+      cudaEventDestroy(c.t_end);
+    }
+  }
+  devs_.clear();
+  ndev_ = 0;
+  inited_ = false;
+  cudaGetLastError();
+  return PARALIA_OK;
+}
+
+int pointer_location(const void* p, bool* pinned) {
+  cudaPointerAttributes at;
+  memset(&at, 0, sizeof(at));
+  cudaError_t e = cudaPointerGetAttributes(&at, p);
+  if (pinned) *pinned = false;
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  if (at.type == cudaMemoryTypeDevice) return at.device;
+  if (at.type == cudaMemoryTypeManaged) return at.device;
+  if (at.type == cudaMemoryTypeHost) {
+    if (pinned) *pinned = true;
+    return -1;
+  }
+  return -1;  // unregistered host memory
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    else
+      cudaGetLastError();
+  });
+  return fn;
+}
+
+int make_tensor_map(CUtensorMap* map, const void* base, int esz, uint64_t d0, uint64_t d1,
+                    uint64_t d2, uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0,
+                    uint32_t box1) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail(PARALIA_ERR_CUDA, "driver entry point cuTensorMapEncodeTiled not found");
+  const cuuint64_t dims[3] = {d0, d1, d2};
+  const cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
+  const cuuint32_t box[3] = {box0, box1, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUtensorMapDataType dt =
+      esz == 8 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT64 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  CUresult r = fn(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(PARALIA_ERR_CUDA,
+                "cuTensorMapEncodeTiled failed (%d): base=%p dims=%llu,%llu,%llu strides=%llu,%llu "
+                "box=%u,%u",
+                (int)r, base, (unsigned long long)d0, (unsigned long long)d1,
+                (unsigned long long)d2, (unsigned long long)stride1_bytes,
+                (unsigned long long)stride2_bytes, box0, box1);
+  return PARALIA_OK;
+}
+
+}  // namespace paralia

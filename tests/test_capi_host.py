@@ -1,0 +1,128 @@
+"""Host-side checks of libparalia.so that need no GPU: the library loads, exports every
+symbol the header declares, and its planner (tile score, tile choice, 2D block
+distribution, autotune with a fixed unit list) agrees with the oracle and with the
+reference's own distribution output."""
+import json
+import re
+import subprocess
+
+import pytest
+
+
+def test_header_symbols_exported(pl):
+    header = (pl.PKG_DIR.parent / "include" / "paralia_c.h").read_text()
+    declared = set(re.findall(r"\b(PARALiA_\w+)\s*\(", header))
+    assert len(declared) >= 25
+    assert declared == set(pl.SIGNATURES), declared ^ set(pl.SIGNATURES)
+    out = subprocess.run(["nm", "-D", "--defined-only", str(pl.LIB_PATH)], check=True,
+                         capture_output=True, text=True).stdout
+    exported = set(re.findall(r" T (PARALiA_\w+)", out))
+    assert declared <= exported, declared - exported
+    handle = pl.lib()
+    for name in declared:
+        assert getattr(handle, name) is not None
+
+
+def test_cpp_compat_symbols_exported(pl):
+    out = subprocess.run(["nm", "-D", "-C", "--defined-only", str(pl.LIB_PATH)], check=True,
+                         capture_output=True, text=True).stdout
+    for name in ("PARALiADgemm(", "PARALiADgemmControled(", "PARALiASgemm(", "PARALiADaxpy(",
+                 "PARALiADdot(", "PARALiADdotControled(", "PARALiADevCacheFree(short)",
+                 "ATC::print_csv()"):
+        assert name in out, name
+
+
+def test_struct_layout_matches_header(pl):
+    # compile a tiny C program against the header and compare sizeof with ctypes
+    import ctypes, tempfile, os
+    src = ('#include <stdio.h>\n#include "paralia_c.h"\n'
+           'int main(){printf("%zu %zu\\n", sizeof(paralia_ctl), sizeof(paralia_report));return 0;}\n')
+    with tempfile.TemporaryDirectory() as d:
+        c = os.path.join(d, "t.c")
+        open(c, "w").write(src)
+        exe = os.path.join(d, "t")
+        subprocess.run(["/usr/bin/gcc", "-I", str(pl.PKG_DIR.parent / "include"), c, "-o", exe],
+                       check=True)
+        a, b = map(int, subprocess.run([exe], check=True, capture_output=True,
+                                       text=True).stdout.split())
+    assert ctypes.sizeof(pl.Ctl) == a
+    assert ctypes.sizeof(pl.Report) == b
+
+
+@pytest.mark.parametrize("dims", [(32768, 32768, 32768), (4096, 4096, 4096), (65536, 65536, 2048),
+                                  (289, 353, 307), (8192, 1024, 4096), (19457, 19457, 19457)])
+@pytest.mark.parametrize("units", [1, 2, 4, 8])
+def test_tile_slowdowns_match_oracle(pl, orc, dims, units):
+    M, N, K = dims
+    for T in (128, 256, 1024, 2048, 2816, 4096, 6144, min(dims)):
+        if T > min(dims):
+            continue
+        got = pl.tile_slowdowns(M, N, K, T, units)
+        want = orc.tile_slowdowns(M, N, K, T, units)
+        assert got == want, (T, got, want)
+
+
+def test_distribution_matches_reference_golden(pl, golden_dir):
+    cases = json.loads((golden_dir / "distribution_ref.json").read_text())["cases"]
+    for c in cases:
+        owner, d1, d2 = pl.distribute_2d(c["units"], c["Mt"], c["Nt"], c["Kt"])
+        assert owner == c["owner"], (c["units"], c["Mt"], c["Nt"], c["Kt"])
+        assert d1 * d2 == c["units"]
+
+
+def test_distribution_matches_oracle_large(pl, orc):
+    for units, Mt, Nt, Kt in [(8, 16, 16, 16), (8, 32, 32, 1), (4, 10, 10, 3), (6, 13, 7, 2)]:
+        owner, d1, d2 = pl.distribute_2d(units, Mt, Nt, Kt)
+        active, want, od1, od2 = orc.distribute_2d(units, Mt, Nt, Kt)
+        assert owner == want and (d1, d2) == (od1, od2)
+        # every k of a C tile on the same unit
+        for ct in range(Mt * Nt):
+            assert len(set(owner[ct * Kt:(ct + 1) * Kt])) == 1
+
+
+def test_autotune_fixed_units_no_gpu(pl, orc):
+    # the model alone, with a caller-fixed unit list: no GPU is touched
+    ctl = pl.make_ctl(units=list(range(8)))
+    rep = pl.autotune_gemm(8, "N", "N", 32768, 32768, 32768, -1, -1, -1, ctl)
+    want_T, want_sl = orc.optimize_tile(32768, 32768, 32768, 8, step=128)
+    assert rep.T == want_T == 2048
+    assert list(rep.T_slowdowns) == want_sl
+    assert rep.active_unit_num == 8 and (rep.grid_d1, rep.grid_d2) == (2, 4)
+    assert rep.subkernel_num == 16 * 16 * 16
+    assert list(rep.subkernels_per_unit[:8]) == [512] * 8
+    assert rep.pred_t > 0
+    # a caller-fixed T is kept
+    rep = pl.autotune_gemm(8, "N", "N", 32768, 32768, 32768, -1, -1, -1,
+                           pl.make_ctl(T=4096, units=[0, 1]))
+    assert rep.T == 4096 and rep.active_unit_num == 2
+
+
+def test_autotune_more_units_predicts_faster(pl):
+    t = []
+    for n in (1, 2, 4, 8):
+        rep = pl.autotune_gemm(8, "N", "N", 32768, 32768, 32768, -1, -1, -1,
+                               pl.make_ctl(units=list(range(n))))
+        t.append(rep.pred_t)
+    assert t[0] > t[1] > t[2] > t[3]
+
+
+def test_invalid_arguments_report_status(pl):
+    with pytest.raises(pl.ParaliaError) as e:
+        pl.tile_slowdowns(0, 1, 1, 1, 1)
+    assert e.value.code == pl.ERR_INVALID_ARG
+    with pytest.raises(pl.ParaliaError) as e:
+        pl.autotune_gemm(3, "N", "N", 8, 8, 8, -1, -1, -1, pl.make_ctl(units=[0]))
+    assert e.value.code == pl.ERR_INVALID_ARG
+    with pytest.raises(pl.ParaliaError) as e:
+        pl.autotune_gemm(8, "X", "N", 8, 8, 8, -1, -1, -1, pl.make_ctl(units=[0]))
+    assert e.value.code == pl.ERR_INVALID_ARG
+    with pytest.raises(pl.ParaliaError) as e:
+        pl.autotune_gemm(8, "N", "N", 8, 8, 8, -1, -1, -1, pl.make_ctl(units=[0, 0]))
+    assert e.value.code == pl.ERR_INVALID_ARG
+
+
+def test_missing_library_fails_loudly(pl, monkeypatch, tmp_path):
+    monkeypatch.setattr(pl, "_lib", None)
+    monkeypatch.setattr(pl, "LIB_PATH", tmp_path / "absent.so")
+    with pytest.raises(pl.LibraryMissing):
+        pl.lib()
