@@ -22,7 +22,9 @@ def _dev(t, dev=0):
 
 
 def _host(t_dev, shape):
-    return np.asfortranarray(t_dev.cpu().numpy().T.reshape(shape[::-1]).T)
+    out = np.asfortranarray(t_dev.cpu().numpy().T)
+    assert out.shape == tuple(shape)
+    return out
 
 
 def _case(orc, ta, tb, M, N, K, pad=0):
