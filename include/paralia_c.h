@@ -163,6 +163,25 @@ int PARALiA_tile_ddot(int dev, void* stream, int64_t N,
                       const double* x, int64_t incx, const double* y, int64_t incy,
                       double* partials, double* result_dev);
 
+/* Dot product that allocates nothing. It has no counterpart in the reference.
+ * For callers that cannot call cudaMalloc where they need the result (inside a
+ * latency-critical loop where an allocation would stall the device, inside a host
+ * application that hands its plugins a fixed memory budget, or while another library
+ * owns the allocator) and therefore cannot provide the scratch PARALiA_tile_ddot asks
+ * for: the per-block partial sums go to a fixed array in the library's own device image
+ * (8 KB, held by every GPU that loads the library until the process exits).
+ *  - N may be at most PARALiA_tile_ddot_noalloc_max_n() (2^31 elements); larger N is
+ *    rejected with PARALIA_ERR_INVALID_ARG.
+ *  - The first call on each GPU looks up the array's device address; make that first
+ *    call before starting any stream capture.
+ *  - All calls on one GPU share the array: two calls whose kernels can overlap on the GPU
+ *    (different streams, no ordering between them) race. Calls on one stream are safe.
+ *  - x, y and result_dev are device pointers on GPU `dev`; the call is asynchronous. */
+int64_t PARALiA_tile_ddot_noalloc_max_n(void);
+int PARALiA_tile_ddot_noalloc(int dev, void* stream, int64_t N,
+                              const double* x, int64_t incx, const double* y, int64_t incy,
+                              double* result_dev);
+
 /* ---- memory and input helpers (reference: CoCoMalloc/CoCoFree/CoCoVecInit/CoCoMemcpy,
  * used at dgemm_runner.cpp:55-69,77) ------------------------------------------------- */
 int PARALiA_malloc(void** ptr, int64_t bytes, int loc);   /* loc -1: pinned host     */

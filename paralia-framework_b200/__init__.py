@@ -128,6 +128,8 @@ SIGNATURES = {
     "PARALiA_tile_daxpy": (C.c_int, [C.c_int, _vp, _i64, _dbl, _vp, _i64, _vp, _i64]),
     "PARALiA_tile_ddot_scratch_bytes": (_i64, [_i64]),
     "PARALiA_tile_ddot": (C.c_int, [C.c_int, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp]),
+    "PARALiA_tile_ddot_noalloc_max_n": (_i64, []),
+    "PARALiA_tile_ddot_noalloc": (C.c_int, [C.c_int, _vp, _i64, _vp, _i64, _vp, _i64, _vp]),
     "PARALiA_malloc": (C.c_int, [C.POINTER(_vp), _i64, C.c_int]),
     "PARALiA_free": (C.c_int, [_vp, C.c_int]),
     "PARALiA_memcpy": (C.c_int, [_vp, C.c_int, _vp, C.c_int, _i64]),
@@ -281,6 +283,20 @@ def tile_ddot_scratch_bytes(N: int) -> int:
 def tile_ddot(dev, N, x, incx, y, incy, partials, result_dev, stream: int = 0) -> None:
     _check(lib().PARALiA_tile_ddot(dev, stream, N, _ptr(x), incx, _ptr(y), incy, _ptr(partials),
                                    _ptr(result_dev)))
+
+
+def tile_ddot_noalloc_max_n() -> int:
+    return int(lib().PARALiA_tile_ddot_noalloc_max_n())
+
+
+def tile_ddot_noalloc(dev, N, x, incx, y, incy, result_dev, stream: int = 0) -> None:
+    """Dot product that allocates nothing: for callers that cannot call cudaMalloc (a
+    latency-critical loop, a plugin with a fixed memory budget) and so cannot supply the
+    scratch ``tile_ddot`` needs. The partial sums live in a fixed array inside the
+    library; N is limited to ``tile_ddot_noalloc_max_n()``; calls that may overlap on
+    one GPU race on that array. No counterpart in the reference."""
+    _check(lib().PARALiA_tile_ddot_noalloc(dev, stream, N, _ptr(x), incx, _ptr(y), incy,
+                                           _ptr(result_dev)))
 
 
 def malloc(nbytes: int, loc: int) -> int:

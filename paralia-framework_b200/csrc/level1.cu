@@ -7,7 +7,12 @@
 // dot. Unit-stride operands on 16-byte boundaries move as 128-bit accesses, four in
 // flight per thread; anything else takes the strided scalar path.
 #include "level1.cuh"
+
+#include <mutex>
+
+#include "../../include/paralia_c.h"
 #include "paralia_rng.h"
+#include "runtime.hpp"
 
 namespace paralia {
 namespace {
@@ -210,4 +215,66 @@ cudaError_t launch_fill_f32(float* p, int64_t n, uint64_t seed, int dist, cudaSt
   return cudaGetLastError();
 }
 
+// ------------------------------------------------------------------------------------
+// Dot product for callers that must not allocate.
+//
+// Some hosts of this library cannot call cudaMalloc at the point where they need a dot
+// product: code running between the warm-up and the steady state of a latency-critical
+// loop where an allocation would synchronise the whole device, plugins that are handed a
+// fixed memory budget by their host application, and code that runs while another
+// library owns the allocator. PARALiA_tile_ddot asks such a caller for a scratch buffer;
+// this variant needs none: the per-block partial sums live in the file-scope device
+// array below, which every GPU that loads the library holds until the process exits
+// (8 KB per GPU).
+namespace {
+
+constexpr int NOALLOC_SCRATCH_DOUBLES = 1024;
+static __device__ __align__(256) double g_ddot_noalloc_scratch[NOALLOC_SCRATCH_DOUBLES];
+
+// Device address of the array on each GPU. In host code the array's name is only a
+// handle for the runtime, not an address a kernel could use, so the address is looked up
+// once per device with that device current.
+std::mutex g_noalloc_mutex;
+double* g_noalloc_ptr[PARALIA_MAX_UNITS] = {};
+
+}  // namespace
 }  // namespace paralia
+
+extern "C" int64_t PARALiA_tile_ddot_noalloc_max_n(void) { return (int64_t)1 << 31; }
+
+extern "C" int PARALiA_tile_ddot_noalloc(int dev, void* stream, int64_t N, const double* x,
+                                         int64_t incx, const double* y, int64_t incy,
+                                         double* result_dev) {
+  using namespace paralia;
+  if (N < 0 || incx <= 0 || incy <= 0) return fail(PARALIA_ERR_INVALID_ARG, "bad N or increment");
+  if (!result_dev || (N > 0 && (!x || !y)))
+    return fail(PARALIA_ERR_INVALID_ARG, "NULL vector or result pointer");
+  if (N > PARALiA_tile_ddot_noalloc_max_n())
+    return fail(PARALIA_ERR_INVALID_ARG,
+                "N = %lld exceeds the %lld elements the allocation-free dot product supports",
+                (long long)N, (long long)PARALiA_tile_ddot_noalloc_max_n());
+  if (l1_grid_blocks(N > 0 ? N : 1) > NOALLOC_SCRATCH_DOUBLES)
+    return fail(PARALIA_ERR_INVALID_ARG, "N = %lld needs more partial sums than the static scratch holds",
+                (long long)N);
+  if (dev < 0 || dev >= PARALIA_MAX_UNITS) return fail(PARALIA_ERR_INVALID_ARG, "GPU id %d out of range", dev);
+  int count = 0;
+  PL_CUDA(cudaGetDeviceCount(&count));
+  if (dev >= count) return fail(PARALIA_ERR_INVALID_ARG, "GPU id %d out of range", dev);
+  DeviceGuard guard;   // cudaGetDevice / cudaSetDevice only
+  PL_CUDA(cudaSetDevice(dev));
+  double* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_noalloc_mutex);
+    if (!g_noalloc_ptr[dev]) {
+      void* p = nullptr;
+      PL_CUDA(cudaGetSymbolAddress(&p, g_ddot_noalloc_scratch));
+      g_noalloc_ptr[dev] = static_cast<double*>(p);
+    }
+    scratch = g_noalloc_ptr[dev];
+  }
+  // Every partial the final kernel reads is written by the first kernel of the same
+  // call, so nothing in the array has to be cleared between calls.
+  PL_CUDA(launch_ddot(N, x, incx, y, incy, scratch, result_dev, static_cast<cudaStream_t>(stream),
+                      nullptr));
+  return PARALIA_OK;
+}
