@@ -54,17 +54,6 @@ def parse_args():
     return ap.parse_args()
 
 
-def device_grid(units: int):
-    """Most-square factorisation by the reference's rule (Subkernel_distributions.cpp:325-336)."""
-    d1 = int(math.sqrt(units))
-    g = d1 + 1
-    while g > 0 and units % g:
-        g -= 1
-    if g == 0:
-        return units, 1
-    return g, units // g
-
-
 # ------------------------------------------------------------------ clocks
 class ClockSampler:
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
@@ -219,11 +208,12 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda:0"))
     pl.init()
 
+    import importlib
+    ranks = importlib.import_module("paralia_framework_b200.ranks")
     n = args.n
-    d1, d2 = device_grid(world)
-    r, c = rank // d2, rank % d2
-    # rank (r, c): rows [r*M/d1, (r+1)*M/d1) x cols [c*N/d2, (c+1)*N/d2) of C
-    Mloc, Nloc, K = n // d1, n // d2, n
+    # rank (r, c) of the D1 x D2 device grid computes its block of C
+    (m0, m1), (n0, n1), (r, c), (d1, d2) = ranks.gemm_block(rank, world, n, n, quantum=128)
+    Mloc, Nloc, K = m1 - m0, n1 - n0, n
     flops_total = 2.0 * n * n * n
     ctl = pl.make_ctl(T=args.tile, units=[0])
 

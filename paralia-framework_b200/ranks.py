@@ -1,0 +1,66 @@
+"""Host-side partition for the one-process-per-GPU launch (torchrun).
+
+The library itself drives every GPU of the box from one process, as the reference does.
+When a launcher starts one process per GPU instead, each rank calls the library on the
+part of the problem its GPU would own in-process: the C block of its cell in the
+D1 x D2 device grid for GEMM (no exchange between ranks), a contiguous chunk for the
+level-1 routines (one scalar all-reduce for DDOT). This module holds that arithmetic;
+it needs no GPU.
+
+Reference: grid rule Autotuner/src/Subkernel_distributions.cpp:325-336, owner of a C
+tile :399, DDOT's final sum Library_scheduler/src/Functions/ddot.cpp:431.
+"""
+from __future__ import annotations
+
+import math
+
+
+def device_grid(units: int) -> tuple[int, int]:
+    """Most-square factorisation units = d1*d2 found by the reference's scan."""
+    d1 = int(math.sqrt(units))
+    if d1 == 0:
+        return 1, units
+    g = d1 + 1
+    while g > 0 and units % g:
+        g -= 1
+    if g == 0:
+        return units, 1
+    return g, units // g
+
+
+def _split(n: int, parts: int, idx: int, quantum: int = 1) -> tuple[int, int]:
+    """[lo, hi) of part idx when n is cut into `parts` runs of whole quanta, the first
+    runs one quantum longer when it does not divide."""
+    q = -(-n // quantum)
+    base, extra = divmod(q, parts)
+    lo = idx * base + min(idx, extra)
+    hi = lo + base + (1 if idx < extra else 0)
+    return min(lo * quantum, n), min(hi * quantum, n)
+
+
+def gemm_block(rank: int, world: int, M: int, N: int, quantum: int = 1):
+    """Rows [m0, m1) and columns [n0, n1) of C that `rank` computes; rank = r*d2 + c."""
+    d1, d2 = device_grid(world)
+    r, c = divmod(rank, d2)
+    m0, m1 = _split(M, d1, r, quantum)
+    n0, n1 = _split(N, d2, c, quantum)
+    return (m0, m1), (n0, n1), (r, c), (d1, d2)
+
+
+def vector_chunk(rank: int, world: int, N: int, quantum: int = 1) -> tuple[int, int]:
+    """Contiguous run [lo, hi) of a length-N vector owned by `rank`."""
+    return _split(N, world, rank, quantum)
+
+
+def allreduce_sum(value: float, device=None) -> float:
+    """Sum of one double over all ranks (DDOT's cross-GPU reduction). Rank partials are
+    added by the backend (NCCL on GPUs, gloo on CPUs); with torch.distributed not
+    initialised the value is returned unchanged."""
+    import torch
+    import torch.distributed as dist
+
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return float(value)
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return float(t.item())
