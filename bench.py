@@ -51,6 +51,9 @@ def parse_args():
     ap.add_argument("--tile", type=int, default=0, help="tile edge T (0 = autotuned)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--inproc", action="store_true",
+                    help="one process drives all --gpus GPUs through the library (the "
+                         "reference's own execution model) instead of one process per GPU")
     return ap.parse_args()
 
 
@@ -216,6 +219,11 @@ def main():
     Mloc, Nloc, K = m1 - m0, n1 - n0, n
     flops_total = 2.0 * n * n * n
     ctl = pl.make_ctl(T=args.tile, units=[0])
+    if args.inproc:
+        assert world == 1, "--inproc is a single-process mode"
+        ngpu = min(args.gpus, pl.device_count())
+        ctl = pl.make_ctl(T=args.tile, units=list(range(ngpu)))
+        d1, d2 = ranks.device_grid(ngpu)
 
     # ---- operands: generated on the GPU by the counter-based generator (same bits as the
     # host generator); the rank's panels are independent seeded streams
@@ -298,7 +306,8 @@ def main():
                               f"path) NN alpha=beta=1 on a {ns}^3 sample of the workload, "
                               f"{ts:.1f} s, {cores} threads")}
         line = {
-            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world,
+            "metric": METRIC, "value": value, "unit": "TFLOP/s",
+            "n_gpus": (len(list(ctl.active_unit_id_list[:ctl.active_unit_num])) if args.inproc else world),
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f64", "data": "synthetic",
@@ -308,7 +317,9 @@ def main():
                 "tile": int(rep.T), "device_grid": [d1, d2],
                 "per_rank_block": [Mloc, Nloc, K],
                 "l2": "operands (>= 3 GiB per GPU) are far larger than the 126 MB L2",
-                "value_placement": "operands resident in HBM", "e2e_placement": "pinned host",
+                "value_placement": ("operands resident in the HBM of GPU 0, one process drives all GPUs"
+                                    if args.inproc else "operands resident in HBM"),
+                "e2e_placement": "pinned host", "launch": "inproc" if args.inproc else "one process per GPU",
             },
             "roofline": {
                 "bound": "tensor", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",

@@ -371,25 +371,21 @@ int enqueue_subkernels<double>(GemmCall<double>& g, int ui, int order_idx, int c
   return PARALIA_OK;
 }
 
-// How many consecutive k of one C tile go into one launch. Operands already on the GPU
-// can run a whole k chain at once (the accumulator stays in registers); streamed tiles
-// start with single-k launches so compute begins as soon as the first pair has landed,
-// and switch to longer chains once the fetch stream is ahead.
+// How many consecutive k tiles of one C tile go into one launch, starting at tile ki0.
+// The split is a function of ki0 alone -- the first launch of every C tile takes one k
+// tile (so that a streamed problem starts computing as soon as one A/B pair has landed),
+// every later launch takes four (the accumulator stays in registers, C makes fewer round
+// trips). Because it depends on nothing else, the arithmetic of a C tile -- and therefore
+// every bit of the result -- is the same whichever GPU runs the tile, however many GPUs
+// take part and wherever the operands live.
 template <typename T>
-int kchain_len(const GemmCall<T>& g, const UnitState& u, int order_idx) {
+int kchain_len(const GemmCall<T>& g, int ki0) {
   static const int forced = [] {
-    const char* e = getenv("PARALIA_KCHAIN");
+    const char* e = getenv("PARALIA_KCHAIN");   // experiments only: changes rounding
     return e ? atoi(e) : 0;
   }();
-  int len;
-  if (forced > 0) len = forced;
-  else {
-    const bool a_here = (g.A.loc == u.dev && u.a_native_ok);
-    const bool b_here = (g.B.loc == u.dev && u.b_native_ok);
-    if (a_here && b_here) len = (int)g.Kt;
-    else if (order_idx < g.exec_streams) len = 1;
-    else len = 4;
-  }
+  (void)g;
+  int len = forced > 0 ? forced : (ki0 == 0 ? 1 : 4);
   len = std::min<int>(len, DG_MAX_PARTS);
   return std::max(len, 1);
 }
@@ -600,7 +596,7 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
       if (u.cursor >= total) continue;
       const int order_idx = (int)(u.cursor / kt_loop);
       const int ki0 = (int)(u.cursor % kt_loop);
-      int ki1 = g.Kt == 0 ? 0 : std::min<int>(kt_loop, ki0 + kchain_len(g, u, order_idx));
+      int ki1 = g.Kt == 0 ? 0 : std::min<int>(kt_loop, ki0 + kchain_len(g, ki0));
       if (g.Kt == 0) {
         rc = enqueue_subkernels<T>(g, ui, order_idx, u.ctiles[order_idx], 0, 0);
         u.cursor = (size_t)(order_idx + 1) * kt_loop;
