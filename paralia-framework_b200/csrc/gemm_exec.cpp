@@ -377,7 +377,9 @@ int enqueue_subkernels<double>(GemmCall<double>& g, int ui, int order_idx, int c
 // every later launch takes four (the accumulator stays in registers, C makes fewer round
 // trips). Because it depends on nothing else, the arithmetic of a C tile -- and therefore
 // every bit of the result -- is the same whichever GPU runs the tile, however many GPUs
-// take part and wherever the operands live.
+// take part and wherever A and B live. (A C tile that lives on the executing GPU is
+// updated in place with beta applied by the first launch instead of the last, which
+// rounds differently from a staged tile.)
 template <typename T>
 int kchain_len(const GemmCall<T>& g, int ki0) {
   static const int forced = [] {
