@@ -189,16 +189,15 @@ def main():
         run_reference_arm(args, rank)
         return
 
-    # one process per GPU: each rank sees exactly its own GPU as device 0
+    # one process per GPU: rank i drives GPU i (LOCAL_RANK) and touches no other GPU
+    dev = local_rank if world > 1 else 0
+    phys = dev
     visible = os.environ.get("CUDA_VISIBLE_DEVICES")
-    phys = local_rank
-    if world > 1:
-        ids = visible.split(",") if visible else [str(i) for i in range(world)]
-        os.environ["CUDA_VISIBLE_DEVICES"] = ids[local_rank]
+    if visible:
         try:
-            phys = int(ids[local_rank])
-        except ValueError:
-            phys = local_rank
+            phys = int(visible.split(",")[dev])
+        except (ValueError, IndexError):
+            phys = dev
 
     import torch
     import torch.distributed as dist
@@ -206,10 +205,15 @@ def main():
 
     pl = entry.load_package()
     pl.lib()   # fails loudly if the CUDA library is missing
-    torch.cuda.set_device(0)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda:0"))
+    torch.cuda.set_device(dev)
+    cuda = f"cuda:{dev}"
     pl.init()
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(cuda))
+        # the ranks form a library group: host-resident tiles are shared over NVLink (CUDA IPC)
+        token = [f"{os.environ.get('MASTER_PORT', '0')}_{os.getpid()}"]
+        dist.broadcast_object_list(token, src=0)
+        pl.group_init(token[0], rank, world, dev)
 
     import importlib
     ranks = importlib.import_module("paralia_framework_b200.ranks")
@@ -218,7 +222,7 @@ def main():
     (m0, m1), (n0, n1), (r, c), (d1, d2) = ranks.gemm_block(rank, world, n, n, quantum=128)
     Mloc, Nloc, K = m1 - m0, n1 - n0, n
     flops_total = 2.0 * n * n * n
-    ctl = pl.make_ctl(T=args.tile, units=[0])
+    ctl = pl.make_ctl(T=args.tile, units=[dev])
     if args.inproc:
         assert world == 1, "--inproc is a single-process mode"
         ngpu = min(args.gpus, pl.device_count())
@@ -228,12 +232,12 @@ def main():
     # ---- operands: generated on the GPU by the counter-based generator (same bits as the
     # host generator); the rank's panels are independent seeded streams
     nA, nB, nC = Mloc * K, K * Nloc, Mloc * Nloc
-    dA = torch.empty(nA, dtype=torch.float64, device="cuda:0")
-    dB = torch.empty(nB, dtype=torch.float64, device="cuda:0")
-    dC = torch.empty(nC, dtype=torch.float64, device="cuda:0")
-    pl.fill_f64(dA, nA, 42 + 1000 * r, 0, 0)
-    pl.fill_f64(dB, nB, 43 + 1000 * c, 0, 0)
-    pl.fill_f64(dC, nC, 44 + 1000 * rank, 0, 0)
+    dA = torch.empty(nA, dtype=torch.float64, device=cuda)
+    dB = torch.empty(nB, dtype=torch.float64, device=cuda)
+    dC = torch.empty(nC, dtype=torch.float64, device=cuda)
+    pl.fill_f64(dA, nA, 42 + 1000 * r, 0, dev)
+    pl.fill_f64(dB, nB, 43 + 1000 * c, 0, dev)
+    pl.fill_f64(dC, nC, 44 + 1000 * rank, 0, dev)
 
     def barrier():
         torch.cuda.synchronize()
@@ -241,31 +245,33 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    gemm = pl.group_dgemm if world > 1 else pl.dgemm
+
     def run_leg(A, B, C, steps, warm):
         launches = h2d = d2h = 0
         dev_ms = 0.0
         for _ in range(warm):
-            pl.dgemm("N", "N", Mloc, Nloc, K, 1.0, A, Mloc, B, K, 1.0, C, Mloc, ctl=ctl)
+            gemm("N", "N", Mloc, Nloc, K, 1.0, A, Mloc, B, K, 1.0, C, Mloc, ctl=ctl)
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(steps):
-            rep = pl.dgemm("N", "N", Mloc, Nloc, K, 1.0, A, Mloc, B, K, 1.0, C, Mloc, ctl=ctl)
+            rep = gemm("N", "N", Mloc, Nloc, K, 1.0, A, Mloc, B, K, 1.0, C, Mloc, ctl=ctl)
             launches += rep.kernel_launches
             h2d += rep.h2d_bytes
             d2h += rep.d2h_bytes
             dev_ms += rep.device_ms
         e1.record()
         barrier()
-        ms = torch.tensor([e0.elapsed_time(e1), dev_ms], dtype=torch.float64, device="cuda:0")
-        cnt = torch.tensor([launches, h2d, d2h], dtype=torch.int64, device="cuda:0")
+        ms = torch.tensor([e0.elapsed_time(e1), dev_ms], dtype=torch.float64, device=cuda)
+        cnt = torch.tensor([launches, h2d, d2h], dtype=torch.int64, device=cuda)
         if world > 1:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
             dist.all_reduce(cnt, op=dist.ReduceOp.SUM)
         return ms[0].item() / steps, ms[1].item() / steps, cnt.tolist(), rep
 
     # ---- FP64 tensor-core peak of this GPU, measured now (register-only DMMA loop)
-    peak_tf = max(pl.bench_dmma_peak(0, 1688, 20000), pl.bench_dmma_peak(0, 16816, 10000))
+    peak_tf = max(pl.bench_dmma_peak(dev, 1688, 20000), pl.bench_dmma_peak(dev, 16816, 10000))
 
     sampler = ClockSampler(phys)
     if rank == 0:
@@ -278,9 +284,9 @@ def main():
     e2e = None
     if not args.no_e2e:
         hA, hB, hC = pl.malloc(nA * 8, -1), pl.malloc(nB * 8, -1), pl.malloc(nC * 8, -1)
-        pl.memcpy(hA, -1, dA, 0, nA * 8)
-        pl.memcpy(hB, -1, dB, 0, nB * 8)
-        pl.memcpy(hC, -1, dC, 0, nC * 8)
+        pl.memcpy(hA, -1, dA, dev, nA * 8)
+        pl.memcpy(hB, -1, dB, dev, nB * 8)
+        pl.memcpy(hC, -1, dC, dev, nC * 8)
         e_steps, e_warm = args.steps, max(1, min(args.warmup, 3))
         e_ms, _, (e_launch, e_h2d, e_d2h), e_rep = run_leg(hA, hB, hC, e_steps, e_warm)
         e2e = {"value": flops_total / (e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
@@ -336,6 +342,7 @@ def main():
         }
         print(json.dumps(line), flush=True)
     if world > 1:
+        pl.group_finalize()
         dist.destroy_process_group()
 
 

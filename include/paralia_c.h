@@ -139,6 +139,26 @@ int PARALiA_ddot(int64_t N, const double* x, int64_t incx, int locx,
                  const double* y, int64_t incy, int locy, double* result,
                  const paralia_ctl* ctl, paralia_report* out);
 
+/* ---- one process per GPU ------------------------------------------------------------
+ * The reference drives all GPUs from one process. Under a launcher that starts one
+ * process per GPU, the processes form a group: rank = r*D2 + c of the D1 x D2 device grid
+ * (the grid rule of Autotuner/src/Subkernel_distributions.cpp:325-336) owns the C block
+ * of grid cell (r, c), as the in-process distribution would give it to that GPU (:399).
+ * PARALiA_group_dgemm is collective: every rank passes ITS row panel of op(A)
+ * (Mloc x K), ITS column panel of op(B) (K x Nloc) and ITS block of C (Mloc x Nloc).
+ * Host-resident A/B tiles then cross the host link once per grid row / column and reach
+ * the other ranks GPU -> GPU through CUDA IPC -- the cross-process form of "a tile cached
+ * on a peer is fetched from the peer". `name` must be the same, unique string on all
+ * ranks (it names a small POSIX shared-memory segment used for the hand-shakes).
+ * No counterpart in the reference (which has no multi-process mode). */
+int PARALiA_group_init(const char* name, int rank, int world, int dev);
+int PARALiA_group_finalize(void);
+int PARALiA_group_dgemm(char TransA, char TransB, int64_t Mloc, int64_t Nloc, int64_t K,
+                        double alpha, const double* A_panel, int64_t ldA, int locA,
+                        const double* B_panel, int64_t ldB, int locB,
+                        double beta, double* C_block, int64_t ldC, int locC,
+                        const paralia_ctl* ctl, paralia_report* out);
+
 /* ---- per-tile kernels on device-resident data ---------------------------------------
  * What the reference reaches through backend_run_operation(params, "Dgemm"|"Sgemm"|
  * "Daxpy"|"Ddot", queue) (Library_scheduler/src/Subkernel.cpp:168,228; parameter blocks

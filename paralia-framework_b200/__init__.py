@@ -121,6 +121,10 @@ SIGNATURES = {
     "PARALiA_daxpy": (C.c_int, [_i64, _dbl, _vp, _i64, C.c_int, _vp, _i64, C.c_int, _ctl_p, _rep_p]),
     "PARALiA_ddot": (C.c_int, [_i64, _vp, _i64, C.c_int, _vp, _i64, C.c_int, C.POINTER(_dbl),
                                _ctl_p, _rep_p]),
+    "PARALiA_group_init": (C.c_int, [C.c_char_p, C.c_int, C.c_int, C.c_int]),
+    "PARALiA_group_finalize": (C.c_int, []),
+    "PARALiA_group_dgemm": (C.c_int, [_chr, _chr, _i64, _i64, _i64, _dbl, _vp, _i64, C.c_int, _vp,
+                                      _i64, C.c_int, _dbl, _vp, _i64, C.c_int, _ctl_p, _rep_p]),
     "PARALiA_tile_dgemm": (C.c_int, [C.c_int, _vp, _chr, _chr, _i64, _i64, _i64, _dbl, _vp, _i64,
                                      _vp, _i64, _dbl, _vp, _i64]),
     "PARALiA_tile_sgemm": (C.c_int, [C.c_int, _vp, _chr, _chr, _i64, _i64, _i64, _flt, _vp, _i64,
@@ -227,6 +231,26 @@ def dgemm(TransA, TransB, M, N, K, alpha, A, ldA, B, ldB, beta, Cm, ldC,
     _check(lib().PARALiA_dgemm(_c(TransA), _c(TransB), M, N, K, alpha, _ptr(A), ldA, locA,
                                _ptr(B), ldB, locB, beta, _ptr(Cm), ldC, locC,
                                C.byref(ctl) if ctl is not None else None, C.byref(rep)))
+    return rep
+
+
+def group_init(name: str, rank: int, world: int, dev: int) -> None:
+    """Join the one-process-per-GPU group `name` as `rank` of `world`, driving GPU `dev`."""
+    _check(lib().PARALiA_group_init(name.encode(), rank, world, dev))
+
+
+def group_finalize() -> None:
+    _check(lib().PARALiA_group_finalize())
+
+
+def group_dgemm(TransA, TransB, Mloc, Nloc, K, alpha, A, ldA, B, ldB, beta, Cm, ldC,
+                locA=LOC_AUTO, locB=LOC_AUTO, locC=LOC_AUTO, ctl: Ctl | None = None) -> Report:
+    """Collective DGEMM of a process group: this rank's row panel of A, column panel of B
+    and block of C (see ``ranks.gemm_block``)."""
+    rep = Report()
+    _check(lib().PARALiA_group_dgemm(_c(TransA), _c(TransB), Mloc, Nloc, K, alpha, _ptr(A), ldA,
+                                     locA, _ptr(B), ldB, locB, beta, _ptr(Cm), ldC, locC,
+                                     C.byref(ctl) if ctl is not None else None, C.byref(rep)))
     return rep
 
 

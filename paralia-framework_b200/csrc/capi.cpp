@@ -9,6 +9,7 @@
 #include "autotune.hpp"
 #include "dgemm_tile.cuh"
 #include "exec.hpp"
+#include "group.hpp"
 #include "level1.cuh"
 #include "paralia_rng.h"
 #include "runtime.hpp"
@@ -92,6 +93,19 @@ int PARALiA_daxpy(int64_t N, double alpha, const double* x, int64_t incx, int lo
 int PARALiA_ddot(int64_t N, const double* x, int64_t incx, int locx, const double* y, int64_t incy,
                  int locy, double* result, const paralia_ctl* ctl, paralia_report* out) {
   return exec_ddot(N, x, incx, locx, y, incy, locy, result, ctl, out);
+}
+
+int PARALiA_group_init(const char* name, int rank, int world, int dev) {
+  return Group::init(name, rank, world, dev);
+}
+int PARALiA_group_finalize(void) { return Group::finalize(); }
+
+int PARALiA_group_dgemm(char TransA, char TransB, int64_t Mloc, int64_t Nloc, int64_t K,
+                        double alpha, const double* A, int64_t ldA, int locA, const double* B,
+                        int64_t ldB, int locB, double beta, double* C, int64_t ldC, int locC,
+                        const paralia_ctl* ctl, paralia_report* out) {
+  return exec_group_dgemm(TransA, TransB, Mloc, Nloc, K, alpha, A, ldA, locA, B, ldB, locB, beta,
+                          C, ldC, locC, ctl, out);
 }
 
 // ------------------------------ per-tile kernels ------------------------------

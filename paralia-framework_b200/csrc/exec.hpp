@@ -10,6 +10,13 @@ int exec_dgemm(char ta, char tb, int64_t M, int64_t N, int64_t K, double alpha, 
                int64_t ldA, int locA, const double* B, int64_t ldB, int locB, double beta,
                double* C, int64_t ldC, int locC, const paralia_ctl* ctl, paralia_report* out);
 
+// Collective over the ranks of the process group (group.hpp): every rank passes its own
+// row panel of A, column panel of B and block of C.
+int exec_group_dgemm(char ta, char tb, int64_t M, int64_t N, int64_t K, double alpha,
+                     const double* A, int64_t ldA, int locA, const double* B, int64_t ldB,
+                     int locB, double beta, double* C, int64_t ldC, int locC,
+                     const paralia_ctl* ctl, paralia_report* out);
+
 int exec_sgemm(char ta, char tb, int64_t M, int64_t N, int64_t K, float alpha, const float* A,
                int64_t ldA, int locA, const float* B, int64_t ldB, int locB, float beta, float* C,
                int64_t ldC, int locC, const paralia_ctl* ctl, paralia_report* out);

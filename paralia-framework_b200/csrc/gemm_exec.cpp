@@ -24,6 +24,7 @@
 #include "runtime.hpp"
 #include "sgemm_tile.cuh"
 #include "exec.hpp"
+#include "group.hpp"
 
 namespace paralia {
 
@@ -73,6 +74,11 @@ struct GemmCall {
   int64_t Mt = 0, Nt = 0, Kt = 0;
   int exec_streams = 4;
   bool peer_fetch = true;
+  // one-process-per-GPU group (null in the default in-process mode)
+  Group* grp = nullptr;
+  bool share_a = false, share_b = false;   // tiles shared inside the grid row / column
+  int nA = 0, nB = 0;                       // fixed block ranges of A and B tiles in group mode
+  bool prefetch_phase = false;              // enqueueing only this rank's home tiles
   std::vector<UnitState> units;
   std::vector<int> ctile_owner;             // C tile -> unit index
   std::vector<std::vector<int>> a_consumers; // per tile-row mi: units that read A(mi,*)
@@ -212,9 +218,48 @@ int ensure_input(GemmCall<T>& g, int ui, bool is_a, int64_t i0, int64_t i1) {
     return PARALIA_OK;
   }
   PL_CUDA(cudaSetDevice(u.dev));
-  PL_TRY(take_block(g, u, &r.block));
-  PL_TRY(rt.get_event(u.dev, &r.ready));
   DeviceCtx& dc = rt.dev(u.dev);
+  if (g.grp && op.loc == -1 && (is_a ? g.share_a : g.share_b)) {
+    // Group mode: the tile is shared between the processes of this rank's grid row (A) or
+    // column (B). Blocks and event slots are fixed functions of the tile so that every
+    // process knows where a peer keeps it.
+    int d1, d2;
+    g.grp->grid(&d1, &d2);
+    const int me = g.grp->rank(), gr = me / d2, gc = me % d2;
+    const int slot = is_a ? (int)tid : g.nA + (int)tid;
+    const int home = is_a ? gr * d2 + (int)((i0 + i1) % d2) : (int)((i0 + i1) % d1) * d2 + gc;
+    if (home == me) {
+      r.block = slot;
+      PL_TRY(rt.get_event(u.dev, &r.ready));
+      PL_TRY(copy_tile_in(g, u, r.block, t.src, op.ld, t, dc.h2d, &g.rep->h2d_bytes));
+      PL_CUDA(cudaEventRecord(r.ready, dc.h2d));
+      PL_CUDA(cudaEventRecord(g.grp->own_event(slot), dc.h2d));
+      u.h2d_tail = r.ready;
+      r.present = true;
+      return PARALIA_OK;
+    }
+    if (g.prefetch_phase) return PARALIA_OK;   // a peer's tile: fetched after the hand-shake
+    r.block = slot;
+    PL_TRY(rt.get_event(u.dev, &r.ready));
+    cudaEvent_t landed;
+    PL_TRY(g.grp->peer_event(home, slot, &landed));
+    PL_CUDA(cudaStreamWaitEvent(dc.p2p, landed, 0));
+    const int peer_slot = is_a ? (int)tid : g.grp->info(home).nA + (int)tid;
+    TileGeom<T> tp = t;
+    if (t.k_is_row) tp.nr = round_up(t.nr, DG_BK); else tp.nc = round_up(t.nc, DG_BK);
+    PL_CUDA(cudaMemcpy2DAsync(g.block_ptr(u, r.block), g.TL * g.esz,
+                              g.grp->peer_slab(home) + (size_t)peer_slot * g.block_bytes(),
+                              g.TL * g.esz, tp.nr * g.esz, tp.nc, cudaMemcpyDefault, dc.p2p));
+    g.rep->p2p_bytes += t.nr * t.nc * g.esz;
+    PL_CUDA(cudaEventRecord(r.ready, dc.p2p));
+    u.p2p_tail = r.ready;
+    r.present = true;
+    return PARALIA_OK;
+  }
+  if (g.prefetch_phase) return PARALIA_OK;
+  if (g.grp) r.block = is_a ? (int)tid : g.nA + (int)tid;   // fixed slots in group mode
+  else PL_TRY(take_block(g, u, &r.block));
+  PL_TRY(rt.get_event(u.dev, &r.ready));
   if (op.loc == -1) {
     // Host-resident tile: one consumer (its "home") pulls it over its host link, the
     // others take it from the home's cache over NVLink.
@@ -249,6 +294,32 @@ int ensure_input(GemmCall<T>& g, int ui, bool is_a, int64_t i0, int64_t i1) {
     u.p2p_tail = r.ready;
   }
   r.present = true;
+  return PARALIA_OK;
+}
+
+// Original C tile of a staged (non-native) C tile, needed by the last k only: fetched
+// into its own block behind the inputs of the tile's first k.
+template <typename T>
+int ensure_csrc(GemmCall<T>& g, int ui, int ct) {
+  Runtime& rt = Runtime::get();
+  UnitState& u = g.units[ui];
+  Resident& rs = u.csrc[ct];
+  if (rs.present || u.c_native || g.beta == (T)0) return PARALIA_OK;
+  DeviceCtx& dc = rt.dev(u.dev);
+  const int64_t mi = ct / g.Nt, ni = ct % g.Nt;
+  PL_CUDA(cudaSetDevice(u.dev));
+  PL_TRY(take_block(g, u, &rs.block));
+  PL_TRY(rt.get_event(u.dev, &rs.ready));
+  const char* src = (const char*)g.C.ptr + (mi * g.Tt + ni * g.Tt * g.C.ld) * g.esz;
+  const int64_t nr = g.mrows(mi), nc = g.ncols(ni);
+  cudaStream_t cs = g.C.loc == -1 ? dc.h2d : dc.p2p;
+  PL_CUDA(cudaMemcpy2DAsync(g.block_ptr(u, rs.block), g.TL * g.esz, src, g.C.ld * g.esz,
+                            nr * g.esz, nc, cudaMemcpyDefault, cs));
+  if (g.C.loc == -1) g.rep->h2d_bytes += nr * nc * g.esz;
+  else g.rep->p2p_bytes += nr * nc * g.esz;
+  PL_CUDA(cudaEventRecord(rs.ready, cs));
+  if (g.C.loc == -1) u.h2d_tail = rs.ready; else u.p2p_tail = rs.ready;
+  rs.present = true;
   return PARALIA_OK;
 }
 
@@ -325,22 +396,7 @@ int enqueue_subkernels<double>(GemmCall<double>& g, int ui, int order_idx, int c
     args.vec_ok = 1;
     if (g.beta != 0.0) {
       Resident& rs = u.csrc[ct];
-      if (first && !rs.present) {
-        // Original C tile, needed only by the last k: fetched behind the first k's inputs.
-        PL_TRY(take_block(g, u, &rs.block));
-        PL_TRY(rt.get_event(u.dev, &rs.ready));
-        TileGeom<double> t;
-        t.src = (const char*)g.C.ptr + (mi * g.Tt + ni * g.Tt * g.C.ld) * g.esz;
-        t.nr = args.M; t.nc = args.N; t.k_is_row = false;
-        cudaStream_t cs = g.C.loc == -1 ? dc.h2d : dc.p2p;
-        PL_CUDA(cudaMemcpy2DAsync(g.block_ptr(u, rs.block), g.TL * g.esz, t.src, g.C.ld * g.esz,
-                                  t.nr * g.esz, t.nc, cudaMemcpyDefault, cs));
-        if (g.C.loc == -1) g.rep->h2d_bytes += t.nr * t.nc * g.esz;
-        else g.rep->p2p_bytes += t.nr * t.nc * g.esz;
-        PL_CUDA(cudaEventRecord(rs.ready, cs));
-        if (g.C.loc == -1) u.h2d_tail = rs.ready; else u.p2p_tail = rs.ready;
-        rs.present = true;
-      }
+      if (first) PL_TRY(ensure_csrc(g, ui, ct));
       if (last) {
         PL_CUDA(cudaStreamWaitEvent(es, rs.ready, 0));
         args.Csrc = (const double*)g.block_ptr(u, rs.block);
@@ -395,7 +451,8 @@ int kchain_len(const GemmCall<T>& g, int ki0) {
 template <typename T>
 int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha, const T* A,
              int64_t ldA, int locA, const T* B, int64_t ldB, int locB, T beta, T* C, int64_t ldC,
-             int locC, const paralia_ctl* ctl, paralia_report* out, const char* func) {
+             int locC, const paralia_ctl* ctl, paralia_report* out, const char* func,
+             Group* grp = nullptr) {
   const double t_call0 = wall_ms();
   paralia_report local_rep;
   paralia_report* rep = out ? out : &local_rep;
@@ -458,6 +515,12 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
     // Tiles that are not the whole problem must be a multiple of the 16-deep pipeline stage.
     const int64_t maxdim = std::max(M, std::max(N, mi_in.K));
     if (eff_ctl.T < maxdim && (eff_ctl.T % DG_BK)) eff_ctl.T = std::max<int64_t>(DG_BK, eff_ctl.T - eff_ctl.T % DG_BK);
+  }
+  if (grp) {
+    // one process, one GPU: the rank's own block of the problem runs on the group's GPU
+    eff_ctl.active_unit_num = 1;
+    eff_ctl.active_unit_id_list[0] = grp->dev();
+    g.grp = grp;
   }
   paralia_report tuned;
   rc = autotune_gemm(mi_in, ngpu, &eff_ctl, &tuned);
@@ -549,6 +612,21 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
       return fail_out(fail(PARALIA_ERR_OUT_OF_MEMORY,
                            "GPU %d needs %zu bytes of tile cache but cache_limit is %lld", u.dev,
                            bytes, (long long)eff_ctl.cache_limit));
+    if (grp) {
+      // collective: agree on sharing, exchange slab handles (group.hpp)
+      g.nA = u.a_native_ok ? 0 : (int)(g.Mt * g.Kt);
+      g.nB = u.b_native_ok ? 0 : (int)(g.Kt * g.Nt);
+      u.next_block = g.nA + g.nB;
+      GroupCallInfo info;
+      memset(&info, 0, sizeof(info));
+      info.Mloc = M; info.Nloc = N; info.K = K; info.T = g.Tt; info.TL = g.TL;
+      info.ta = g.A.trans; info.tb = g.B.trans; info.esz = g.esz;
+      info.a_host = g.A.loc == -1 && K > 0; info.b_host = g.B.loc == -1 && K > 0;
+      info.nA = g.nA; info.nB = g.nB;
+      info.want_share = g.peer_fetch ? 1 : 0;
+      rc = grp->begin_call(info, bytes, &alloc_ms, &g.share_a, &g.share_b);
+      if (rc != PARALIA_OK) return fail_out(rc);
+    }
     if (bytes > 0) {
       rc = rt.ensure_slab(u.dev, bytes, &alloc_ms);
       if (rc != PARALIA_OK) return fail_out(rc);
@@ -586,10 +664,32 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
     cudaStreamWaitEvent(dc.p2p, dc.t_begin, 0);
     cudaStreamWaitEvent(dc.d2h, dc.t_begin, 0);
   }
+  const int kt_loop = (int)std::max<int64_t>(g.Kt, 1);
+  if (grp) {
+    // Group mode, phase 1: enqueue the host fetches of the tiles this rank is the home of
+    // (in the order its own kernels will want them) and record their inter-process
+    // events; after the barrier every rank may wait on any peer's events.
+    if ((g.share_a || g.share_b) && g.Kt > 0) {
+      g.prefetch_phase = true;
+      UnitState& u = g.units[0];
+      for (size_t oi = 0; oi < u.ctiles.size() && rc == PARALIA_OK; ++oi) {
+        const int64_t mi = u.ctiles[oi] / g.Nt, ni = u.ctiles[oi] % g.Nt;
+        for (int64_t ki = 0; ki < g.Kt && rc == PARALIA_OK; ++ki) {
+          rc = ensure_input(g, 0, true, mi, ki);
+          if (rc == PARALIA_OK) rc = ensure_input(g, 0, false, ki, ni);
+          // keep the host link's queue in the order of use: the original C tile rides
+          // behind the first k's inputs, exactly as in the single-process order
+          if (rc == PARALIA_OK && ki == 0) rc = ensure_csrc(g, 0, u.ctiles[oi]);
+        }
+      }
+      g.prefetch_phase = false;
+    }
+    const int brc = grp->barrier();
+    if (rc == PARALIA_OK) rc = brc;
+  }
   // Round-robin over the GPUs, one launch per turn (the reference's fire loop walks the
   // devices the same way, dgemm.cpp:516-544).
-  const int kt_loop = (int)std::max<int64_t>(g.Kt, 1);
-  bool work_left = true;
+  bool work_left = rc == PARALIA_OK;
   while (work_left) {
     work_left = false;
     for (int ui = 0; ui < active; ++ui) {
@@ -641,6 +741,11 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
   }
   if (rc == PARALIA_OK)
     for (int ui = 0; ui < active && rc == PARALIA_OK; ++ui) rc = rt.check_status(g.units[ui].dev);
+  if (grp) {
+    // no rank may start overwriting its slab while a peer still copies out of it
+    const int brc = grp->barrier();
+    if (rc == PARALIA_OK) rc = brc;
+  }
   cleanup_pins();
   rep->device_ms = dev_ms;
   rep->host_ms = wall_ms() - t_call0;
@@ -654,6 +759,16 @@ int exec_dgemm(char ta, char tb, int64_t M, int64_t N, int64_t K, double alpha, 
                double* C, int64_t ldC, int locC, const paralia_ctl* ctl, paralia_report* out) {
   return run_gemm<double>(ta, tb, M, N, K, alpha, A, ldA, locA, B, ldB, locB, beta, C, ldC, locC,
                           ctl, out, "Dgemm");
+}
+
+int exec_group_dgemm(char ta, char tb, int64_t M, int64_t N, int64_t K, double alpha,
+                     const double* A, int64_t ldA, int locA, const double* B, int64_t ldB,
+                     int locB, double beta, double* C, int64_t ldC, int locC,
+                     const paralia_ctl* ctl, paralia_report* out) {
+  Group* grp = Group::current();
+  if (!grp) return fail(PARALIA_ERR_INVALID_ARG, "PARALiA_group_init has not been called");
+  return run_gemm<double>(ta, tb, M, N, K, alpha, A, ldA, locA, B, ldB, locB, beta, C, ldC, locC,
+                          ctl, out, "Dgemm", grp);
 }
 
 }  // namespace paralia

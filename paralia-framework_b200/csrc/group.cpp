@@ -1,0 +1,272 @@
+#include "group.hpp"
+
+#include <fcntl.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <atomic>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "autotune.hpp"
+#include "runtime.hpp"
+
+namespace paralia {
+
+namespace {
+constexpr uint32_t SHM_MAGIC = 0x50414c47u;  // "PALG"
+constexpr double BARRIER_TIMEOUT_MS = 60000.0;
+Group* g_group = nullptr;
+}  // namespace
+
+struct Group::Shm {
+  std::atomic<uint32_t> magic;
+  std::atomic<uint32_t> arrived;
+  std::atomic<uint32_t> generation;
+  std::atomic<uint32_t> attached;
+  int32_t world;
+  struct Rank {
+    cudaIpcMemHandle_t slab_handle;
+    uint64_t slab_gen;        // 0 = no slab exported
+    uint64_t slab_bytes;
+    int32_t will_realloc;
+    int32_t failed;
+    int32_t share_a_ok, share_b_ok;   // this rank's own verdict for the current call
+    GroupCallInfo call;
+    cudaIpcEventHandle_t ev[GROUP_MAX_EVENTS];
+  } ranks[GROUP_MAX_RANKS];
+};
+
+Group* Group::current() { return g_group; }
+
+const GroupCallInfo& Group::info(int peer) const { return shm_->ranks[peer].call; }
+
+int Group::init(const char* name, int rank, int world, int dev) {
+  if (g_group) return fail(PARALIA_ERR_INVALID_ARG, "a group is already initialised in this process");
+  if (!name || world < 1 || world > GROUP_MAX_RANKS || rank < 0 || rank >= world)
+    return fail(PARALIA_ERR_INVALID_ARG, "bad group arguments (rank %d of %d)", rank, world);
+  Runtime& rt = Runtime::get();
+  PL_TRY(rt.init());
+  DeviceGuard guard;
+  PL_TRY(rt.ensure_device(dev));
+  Group* g = new (std::nothrow) Group();
+  if (!g) return fail(PARALIA_ERR_OUT_OF_MEMORY, "out of host memory");
+  g->rank_ = rank;
+  g->world_ = world;
+  g->dev_ = dev;
+  device_grid(world, &g->d1_, &g->d2_);
+  snprintf(g->shm_name_, sizeof(g->shm_name_), "/paralia_%s", name);
+  g->shm_bytes_ = sizeof(Shm);
+  int fd = -1;
+  const double t0 = wall_ms();
+  if (rank == 0) {
+    shm_unlink(g->shm_name_);
+    fd = shm_open(g->shm_name_, O_CREAT | O_EXCL | O_RDWR, 0600);
+    if (fd < 0 || ftruncate(fd, (off_t)g->shm_bytes_) != 0) {
+      if (fd >= 0) close(fd);
+      delete g;
+      return fail(PARALIA_ERR_CUDA, "cannot create the shared segment %s", g->shm_name_);
+    }
+  } else {
+    while ((fd = shm_open(g->shm_name_, O_RDWR, 0600)) < 0) {
+      if (wall_ms() - t0 > BARRIER_TIMEOUT_MS) {
+        delete g;
+        return fail(PARALIA_ERR_TIMEOUT, "rank 0 never created the shared segment");
+      }
+      usleep(1000);
+    }
+    struct stat st;
+    while (fstat(fd, &st) == 0 && (size_t)st.st_size < g->shm_bytes_) {
+      if (wall_ms() - t0 > BARRIER_TIMEOUT_MS) {
+        close(fd);
+        delete g;
+        return fail(PARALIA_ERR_TIMEOUT, "the shared segment never reached its size");
+      }
+      usleep(1000);
+    }
+  }
+  void* p = mmap(nullptr, g->shm_bytes_, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+  close(fd);
+  if (p == MAP_FAILED) {
+    delete g;
+    return fail(PARALIA_ERR_CUDA, "cannot map the shared segment");
+  }
+  g->shm_ = static_cast<Shm*>(p);
+  if (rank == 0) {
+    memset(p, 0, g->shm_bytes_);
+    g->shm_->world = world;
+    g->shm_->magic.store(SHM_MAGIC, std::memory_order_release);
+  } else {
+    while (g->shm_->magic.load(std::memory_order_acquire) != SHM_MAGIC) {
+      if (wall_ms() - t0 > BARRIER_TIMEOUT_MS) {
+        munmap(p, g->shm_bytes_);
+        delete g;
+        return fail(PARALIA_ERR_TIMEOUT, "rank 0 never initialised the shared segment");
+      }
+      usleep(200);
+    }
+  }
+  // Inter-process events, one per shareable tile slot, exported once.
+  PL_CUDA(cudaSetDevice(dev));
+  for (int i = 0; i < GROUP_MAX_EVENTS; ++i) {
+    PL_CUDA(cudaEventCreateWithFlags(&g->own_ev_[i], cudaEventDisableTiming | cudaEventInterprocess));
+    PL_CUDA(cudaIpcGetEventHandle(&g->shm_->ranks[rank].ev[i], g->own_ev_[i]));
+  }
+  g->shm_->attached.fetch_add(1);
+  g_group = g;
+  int rc = g->barrier();
+  if (rc != PARALIA_OK) return rc;
+  if (rank == 0) shm_unlink(g->shm_name_);  // every rank has it mapped; the name can go
+  return PARALIA_OK;
+}
+
+int Group::finalize() {
+  Group* g = g_group;
+  if (!g) return PARALIA_OK;
+  DeviceGuard guard;
+  cudaSetDevice(g->dev_);
+  cudaDeviceSynchronize();
+  g->barrier();   // nobody is still reading a peer's slab
+  for (int p = 0; p < g->world_; ++p) {
+    if (g->peer_slab_[p]) cudaIpcCloseMemHandle(g->peer_slab_[p]);
+    for (int i = 0; i < GROUP_MAX_EVENTS; ++i)
+      if (g->peer_ev_[p][i]) cudaEventDestroy(g->peer_ev_[p][i]);
+  }
+  g->barrier();   // every importer has closed its mappings before slabs may be freed
+  for (int i = 0; i < GROUP_MAX_EVENTS; ++i)
+    if (g->own_ev_[i]) cudaEventDestroy(g->own_ev_[i]);
+  munmap(g->shm_, g->shm_bytes_);
+  cudaGetLastError();
+  delete g;
+  g_group = nullptr;
+  return PARALIA_OK;
+}
+
+int Group::barrier() {
+  if (world_ == 1) return PARALIA_OK;
+  const uint32_t gen = shm_->generation.load(std::memory_order_acquire);
+  if (shm_->arrived.fetch_add(1, std::memory_order_acq_rel) + 1 == (uint32_t)world_) {
+    shm_->arrived.store(0, std::memory_order_relaxed);
+    shm_->generation.store(gen + 1, std::memory_order_release);
+    return PARALIA_OK;
+  }
+  const double t0 = wall_ms();
+  uint32_t spins = 0;
+  while (shm_->generation.load(std::memory_order_acquire) == gen) {
+    if ((++spins & 1023u) == 0) {
+      if (wall_ms() - t0 > BARRIER_TIMEOUT_MS)
+        return fail(PARALIA_ERR_TIMEOUT, "rank %d: a group barrier timed out (a rank is missing)",
+                    rank_);
+      usleep(20);
+    }
+  }
+  return PARALIA_OK;
+}
+
+int Group::peer_event(int peer, int slot, cudaEvent_t* ev) {
+  if (peer < 0 || peer >= world_ || slot < 0 || slot >= GROUP_MAX_EVENTS)
+    return fail(PARALIA_ERR_INVALID_ARG, "bad peer event (%d, %d)", peer, slot);
+  if (!peer_ev_[peer][slot])
+    PL_CUDA(cudaIpcOpenEventHandle(&peer_ev_[peer][slot], shm_->ranks[peer].ev[slot]));
+  *ev = peer_ev_[peer][slot];
+  return PARALIA_OK;
+}
+
+int Group::open_peer_slabs() {
+  for (int p = 0; p < world_; ++p) {
+    if (p == rank_) continue;
+    const Shm::Rank& r = shm_->ranks[p];
+    if (r.slab_gen == peer_gen_[p]) continue;
+    if (peer_slab_[p]) {   // normally closed already in begin_call
+      PL_CUDA(cudaIpcCloseMemHandle(peer_slab_[p]));
+      peer_slab_[p] = nullptr;
+    }
+    if (r.slab_gen != 0) {
+      // A slab that cannot be mapped only switches sharing with that rank off.
+      cudaError_t e = cudaIpcOpenMemHandle(&peer_slab_[p], r.slab_handle,
+                                           cudaIpcMemLazyEnablePeerAccess);
+      if (e != cudaSuccess) {
+        cudaGetLastError();
+        peer_slab_[p] = nullptr;
+      }
+    }
+    peer_gen_[p] = r.slab_gen;
+  }
+  return PARALIA_OK;
+}
+
+int Group::begin_call(const GroupCallInfo& mine, size_t slab_bytes, double* alloc_ms,
+                      bool* share_a, bool* share_b) {
+  Runtime& rt = Runtime::get();
+  DeviceCtx& dc = rt.dev(dev_);
+  Shm::Rank& me = shm_->ranks[rank_];
+  PL_CUDA(cudaSetDevice(dev_));
+  // 1. say whether the slab is about to be replaced, so importers unmap it first
+  me.call = mine;
+  me.will_realloc = dc.slab_bytes < slab_bytes ? 1 : 0;
+  PL_TRY(barrier());
+  for (int p = 0; p < world_; ++p)
+    if (p != rank_ && shm_->ranks[p].will_realloc && peer_slab_[p]) {
+      PL_CUDA(cudaIpcCloseMemHandle(peer_slab_[p]));
+      peer_slab_[p] = nullptr;
+      peer_gen_[p] = 0;
+    }
+  PL_TRY(barrier());
+  // 2. (re)allocate and export
+  int rc = rt.ensure_slab(dev_, slab_bytes, alloc_ms);
+  me.failed = rc != PARALIA_OK;
+  if (rc == PARALIA_OK && dc.slab && dc.slab_gen != my_gen_) {
+    cudaError_t e = cudaIpcGetMemHandle(&me.slab_handle, dc.slab);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      me.failed = 1;
+      rc = fail(PARALIA_ERR_CUDA, "cudaIpcGetMemHandle: %s", cudaGetErrorString(e));
+    } else {
+      my_gen_ = dc.slab_gen;
+      // generations of different ranks never collide with "0 = nothing exported"
+      me.slab_gen = my_gen_ + 1;
+      me.slab_bytes = dc.slab_bytes;
+    }
+  }
+  int rcb = barrier();
+  if (rc != PARALIA_OK) return rc;
+  PL_TRY(rcb);
+  for (int p = 0; p < world_; ++p)
+    if (shm_->ranks[p].failed)
+      return fail(PARALIA_ERR_OUT_OF_MEMORY, "rank %d could not set up its tile cache", p);
+  PL_TRY(open_peer_slabs());
+  // 3. sharing is on for an operand only if every rank of the grid row (A) / column (B)
+  //    runs the same tiling of the same panel
+  const int r = rank_ / d2_, c = rank_ % d2_;
+  bool sa = mine.a_host && mine.want_share && d2_ > 1 && mine.nA + mine.nB <= GROUP_MAX_EVENTS;
+  bool sb = mine.b_host && mine.want_share && d1_ > 1 && mine.nA + mine.nB <= GROUP_MAX_EVENTS;
+  for (int cc = 0; cc < d2_ && sa; ++cc) {
+    const GroupCallInfo& o = shm_->ranks[r * d2_ + cc].call;
+    sa = o.a_host && o.want_share && o.T == mine.T && o.TL == mine.TL && o.Mloc == mine.Mloc &&
+         o.K == mine.K && o.ta == mine.ta && o.esz == mine.esz && o.nA == mine.nA &&
+         o.nA + o.nB <= GROUP_MAX_EVENTS &&
+         (r * d2_ + cc == rank_ || peer_slab_[r * d2_ + cc] != nullptr);
+  }
+  for (int rr = 0; rr < d1_ && sb; ++rr) {
+    const GroupCallInfo& o = shm_->ranks[rr * d2_ + c].call;
+    sb = o.b_host && o.want_share && o.T == mine.T && o.TL == mine.TL && o.Nloc == mine.Nloc &&
+         o.K == mine.K && o.tb == mine.tb && o.esz == mine.esz && o.nB == mine.nB &&
+         o.nA + o.nB <= GROUP_MAX_EVENTS &&
+         (rr * d2_ + c == rank_ || peer_slab_[rr * d2_ + c] != nullptr);
+  }
+  // 4. the verdict must be the same on every rank of the row / column: a rank that
+  //    shares waits for events that a rank that does not share would never record
+  me.share_a_ok = sa;
+  me.share_b_ok = sb;
+  PL_TRY(barrier());
+  for (int cc = 0; cc < d2_; ++cc) sa = sa && shm_->ranks[r * d2_ + cc].share_a_ok;
+  for (int rr = 0; rr < d1_; ++rr) sb = sb && shm_->ranks[rr * d2_ + c].share_b_ok;
+  *share_a = sa;
+  *share_b = sb;
+  return PARALIA_OK;
+}
+
+}  // namespace paralia

@@ -46,25 +46,6 @@ int Runtime::init() {
   ndev_ = n;
   devs_.assign(n, DeviceCtx());
   for (int d = 0; d < n; ++d) devs_[d].dev = d;
-  // Peer access between every pair (reference: CoCoEnableLinks for every location,
-  // dgemm.cpp:423). On an NVSwitch box every pair is reachable at the same bandwidth.
-  for (int a = 0; a < n; ++a) {
-    PL_CUDA(cudaSetDevice(a));
-    for (int b = 0; b < n; ++b) {
-      if (a == b) continue;
-      int can = 0;
-      PL_CUDA(cudaDeviceCanAccessPeer(&can, a, b));
-      if (can) {
-        cudaError_t pe = cudaDeviceEnablePeerAccess(b, 0);
-        if (pe == cudaErrorPeerAccessAlreadyEnabled) {
-          cudaGetLastError();
-          pe = cudaSuccess;
-        }
-        peer_[a][b] = (pe == cudaSuccess);
-        if (pe != cudaSuccess) cudaGetLastError();
-      }
-    }
-  }
   inited_ = true;
   return PARALIA_OK;
 }
@@ -85,6 +66,25 @@ int Runtime::ensure_device(int d) {
   PL_CUDA(cudaMemset(c.status_dev, 0, sizeof(int)));
   PL_CUDA(dgemm_tile_configure());
   PL_CUDA(sgemm_tile_configure());
+  // Peer access between this GPU and every GPU already in use (reference: CoCoEnableLinks
+  // for every location, dgemm.cpp:423). Done pairwise as GPUs come into use, so a process
+  // that drives a single GPU never creates a context on the others. On an NVSwitch box
+  // every pair is reachable at the same bandwidth.
+  for (int o = 0; o < ndev_; ++o) {
+    if (o == d || !devs_[o].ready) continue;
+    for (int dir = 0; dir < 2; ++dir) {
+      const int a = dir ? o : d, b = dir ? d : o;
+      int can = 0;
+      PL_CUDA(cudaSetDevice(a));
+      PL_CUDA(cudaDeviceCanAccessPeer(&can, a, b));
+      if (!can) continue;
+      cudaError_t pe = cudaDeviceEnablePeerAccess(b, 0);
+      if (pe == cudaErrorPeerAccessAlreadyEnabled) pe = cudaSuccess;
+      cudaGetLastError();
+      peer_[a][b] = (pe == cudaSuccess);
+    }
+  }
+  PL_CUDA(cudaSetDevice(d));
   c.ready = true;
   return PARALIA_OK;
 }
@@ -108,6 +108,7 @@ int Runtime::ensure_slab(int d, size_t bytes, double* alloc_ms) {
                 bytes, cudaGetErrorString(e));
   }
   c.slab_bytes = bytes;
+  ++c.slab_gen;
   if (alloc_ms) *alloc_ms += wall_ms() - t0;
   return PARALIA_OK;
 }
@@ -121,6 +122,7 @@ int Runtime::free_slab(int d) {
   PL_CUDA(cudaFree(c.slab));
   c.slab = nullptr;
   c.slab_bytes = 0;
+  ++c.slab_gen;
   return PARALIA_OK;
 }
 

@@ -49,6 +49,7 @@ struct DeviceCtx {
   // sized by ManageCachesDgemm, Library_scheduler/src/Functions/dgemm.cpp:23-121).
   void* slab = nullptr;
   size_t slab_bytes = 0;
+  uint64_t slab_gen = 0;   // bumped whenever the slab is (re)allocated or freed
   // Device word the kernels write a KERR_* code into when a bounded wait gives up.
   int* status_dev = nullptr;
   // Scratch for dot products: per-block partials and per-tile results.
