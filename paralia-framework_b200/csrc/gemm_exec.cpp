@@ -79,6 +79,10 @@ struct GemmCall {
   bool share_a = false, share_b = false;   // tiles shared inside the grid row / column
   int nA = 0, nB = 0;                       // fixed block ranges of A and B tiles in group mode
   bool prefetch_phase = false;              // enqueueing only this rank's home tiles
+  // Write-backs held until the unit's host->GPU stream has drained (see run_gemm).
+  bool defer_wb = false;
+  struct PendingWb { int ui; cudaEvent_t done; char* dst; int64_t dst_ld; const char* src; int64_t rows, cols; };
+  std::vector<PendingWb> pending_wb;
   std::vector<UnitState> units;
   std::vector<int> ctile_owner;             // C tile -> unit index
   std::vector<std::vector<int>> a_consumers; // per tile-row mi: units that read A(mi,*)
@@ -256,7 +260,6 @@ int ensure_input(GemmCall<T>& g, int ui, bool is_a, int64_t i0, int64_t i1) {
     r.present = true;
     return PARALIA_OK;
   }
-  if (g.prefetch_phase) return PARALIA_OK;
   if (g.grp) r.block = is_a ? (int)tid : g.nA + (int)tid;   // fixed slots in group mode
   else PL_TRY(take_block(g, u, &r.block));
   PL_TRY(rt.get_event(u.dev, &r.ready));
@@ -331,6 +334,20 @@ template <>
 int launch_tile<double>(const CUtensorMap& mapA, const CUtensorMap& mapB, const DgemmArgs& args,
                         bool a_kc, bool b_kc, cudaStream_t s) {
   PL_CUDA(launch_dgemm_tile(mapA, mapB, args, a_kc, b_kc, s));
+  return PARALIA_OK;
+}
+
+// Copy a finished C tile from its cache block to where C lives, after its last kernel.
+template <typename T>
+int issue_writeback(GemmCall<T>& g, const typename GemmCall<T>::PendingWb& wb) {
+  UnitState& u = g.units[wb.ui];
+  DeviceCtx& dc = Runtime::get().dev(u.dev);
+  PL_CUDA(cudaSetDevice(u.dev));
+  PL_CUDA(cudaStreamWaitEvent(dc.d2h, wb.done, 0));
+  PL_CUDA(cudaMemcpy2DAsync(wb.dst, wb.dst_ld * g.esz, wb.src, g.TL * g.esz,
+                            (size_t)wb.rows * g.esz, wb.cols, cudaMemcpyDefault, dc.d2h));
+  if (g.C.loc == -1) g.rep->d2h_bytes += wb.rows * wb.cols * g.esz;
+  else g.rep->p2p_bytes += wb.rows * wb.cols * g.esz;
   return PARALIA_OK;
 }
 
@@ -417,12 +434,11 @@ int enqueue_subkernels<double>(GemmCall<double>& g, int ui, int order_idx, int c
   u.exec_tail[sidx] = done;
   if (last && !rc.native) {
     // Write the finished tile back to where C lives (reference: WBTileMap, dgemm.cpp:583).
-    PL_CUDA(cudaStreamWaitEvent(dc.d2h, done, 0));
     char* dst = (char*)g.C.ptr + (mi * g.Tt + ni * g.Tt * g.C.ld) * g.esz;
-    PL_CUDA(cudaMemcpy2DAsync(dst, g.C.ld * g.esz, g.block_ptr(u, rc.block), g.TL * g.esz,
-                              (size_t)args.M * g.esz, args.N, cudaMemcpyDefault, dc.d2h));
-    if (g.C.loc == -1) g.rep->d2h_bytes += (int64_t)args.M * args.N * g.esz;
-    else g.rep->p2p_bytes += (int64_t)args.M * args.N * g.esz;
+    typename GemmCall<double>::PendingWb wb{ui, done, dst, g.C.ld, g.block_ptr(u, rc.block),
+                                           (int64_t)args.M, (int64_t)args.N};
+    if (g.defer_wb && g.C.loc == -1) g.pending_wb.push_back(wb);
+    else PL_TRY(issue_writeback(g, wb));
   }
   return PARALIA_OK;
 }
@@ -664,6 +680,15 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
     cudaStreamWaitEvent(dc.p2p, dc.t_begin, 0);
     cudaStreamWaitEvent(dc.d2h, dc.t_begin, 0);
   }
+  // With four or more GPUs pulling from the host at once, this class of host delivers far
+  // less in both directions together than in one direction alone (measured on an
+  // 8 x B200 box: 185 GB/s host->GPU alone, 63 + 63 GB/s with GPU->host traffic running),
+  // so C tiles are written back only after the unit's input stream has drained; with
+  // fewer GPUs the two directions overlap well and tiles go back as they finish.
+  {
+    const char* e = getenv("PARALIA_DEFER_WB");
+    g.defer_wb = e ? atoi(e) != 0 : (grp ? grp->world() : active) >= 4;
+  }
   const int kt_loop = (int)std::max<int64_t>(g.Kt, 1);
   if (grp) {
     // Group mode, phase 1: enqueue the host fetches of the tiles this rank is the home of
@@ -710,6 +735,19 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
       if (u.cursor < total) work_left = true;
     }
     if (rc != PARALIA_OK) break;
+  }
+  if (rc == PARALIA_OK && !g.pending_wb.empty()) {
+    for (int ui = 0; ui < active; ++ui) {
+      UnitState& u = g.units[ui];
+      if (u.h2d_tail) {
+        cudaSetDevice(u.dev);
+        cudaStreamWaitEvent(rt.dev(u.dev).d2h, u.h2d_tail, 0);
+      }
+    }
+    for (const auto& wb : g.pending_wb) {
+      rc = issue_writeback(g, wb);
+      if (rc != PARALIA_OK) break;
+    }
   }
   // ------------------------------ join ------------------------------
   double dev_ms = 0.0;
