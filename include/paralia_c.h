@@ -239,6 +239,8 @@ int PARALiA_bench_dmma_peak(int dev, int shape, int iters, double* tflops);
 /* Time `reps` launches of the tile DGEMM on square T; returns mean seconds. */
 int PARALiA_bench_tile_dgemm(int dev, char TransA, char TransB, int64_t T, int reps,
                              double* mean_s);
+/* Same for the FP32 kernel: operands are packed once, only the GEMM kernel is timed. */
+int PARALiA_bench_tile_sgemm(int dev, int64_t T, int reps, double* mean_s);
 /* Time a strided 2-D tile copy dim x dim doubles src_loc -> dst_loc; mean seconds. */
 int PARALiA_bench_link(int dst_loc, int src_loc, int64_t dim, int reps, double* mean_s);
 

@@ -147,6 +147,7 @@ SIGNATURES = {
     "PARALiA_load_database": (C.c_int, [C.c_char_p]),
     "PARALiA_bench_dmma_peak": (C.c_int, [C.c_int, C.c_int, C.c_int, C.POINTER(_dbl)]),
     "PARALiA_bench_tile_dgemm": (C.c_int, [C.c_int, _chr, _chr, _i64, C.c_int, C.POINTER(_dbl)]),
+    "PARALiA_bench_tile_sgemm": (C.c_int, [C.c_int, _i64, C.c_int, C.POINTER(_dbl)]),
     "PARALiA_bench_link": (C.c_int, [C.c_int, C.c_int, _i64, C.c_int, C.POINTER(_dbl)]),
 }
 
@@ -385,6 +386,12 @@ def bench_dmma_peak(dev=0, shape=1688, iters=20000) -> float:
 def bench_tile_dgemm(dev, TransA, TransB, T, reps) -> float:
     v = C.c_double()
     _check(lib().PARALiA_bench_tile_dgemm(dev, _c(TransA), _c(TransB), T, reps, C.byref(v)))
+    return v.value
+
+
+def bench_tile_sgemm(dev, T, reps) -> float:
+    v = C.c_double()
+    _check(lib().PARALiA_bench_tile_sgemm(dev, T, reps, C.byref(v)))
     return v.value
 
 

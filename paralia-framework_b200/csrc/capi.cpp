@@ -418,6 +418,48 @@ int PARALiA_bench_tile_dgemm(int dev, char TransA, char TransB, int64_t T, int r
   return rc;
 }
 
+int PARALiA_bench_tile_sgemm(int dev, int64_t T, int reps, double* mean_s) {
+  if (!mean_s || reps <= 0 || T <= 0 || T > 32768) return fail(PARALIA_ERR_INVALID_ARG, "bad bench arguments");
+  DeviceGuard guard;
+  PL_TRY(setup_device(dev));
+  const size_t n = (size_t)T * T;
+  float *A = nullptr, *B = nullptr, *C = nullptr;
+  void *pa = nullptr, *pb = nullptr;
+  PL_CUDA(cudaMalloc(&A, n * 4));
+  PL_CUDA(cudaMalloc(&B, n * 4));
+  PL_CUDA(cudaMalloc(&C, n * 4));
+  PL_CUDA(cudaMalloc(&pa, sgemm_packed_bytes(T, T, SG_BM)));
+  PL_CUDA(cudaMalloc(&pb, sgemm_packed_bytes(T, T, SG_BN)));
+  PL_CUDA(launch_fill_f32(A, n, 42, 1, nullptr));
+  PL_CUDA(launch_fill_f32(B, n, 43, 1, nullptr));
+  PL_CUDA(cudaMemset(C, 0, n * 4));
+  PL_CUDA(launch_sgemm_pack(A, T, false, (int)T, (int)T, SG_BM, pa, nullptr));
+  PL_CUDA(launch_sgemm_pack(B, T, true, (int)T, (int)T, SG_BN, pb, nullptr));
+  SgemmArgs args;
+  memset(&args, 0, sizeof(args));
+  args.C = C; args.ldc = T; args.alpha = 1.0f; args.beta_c = 0.5f;
+  args.M = (int32_t)T; args.N = (int32_t)T;
+  args.status = Runtime::get().dev(dev).status_dev;
+  args.nparts = 1;
+  args.parts[0].a_packed = pa; args.parts[0].b_packed = pb; args.parts[0].klen = (int32_t)T;
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  cudaEvent_t e0, e1;
+  PL_CUDA(cudaEventCreate(&e0));
+  PL_CUDA(cudaEventCreate(&e1));
+  for (int i = 0; i < 2; ++i) PL_CUDA(launch_sgemm_tile(args, sms, nullptr));
+  PL_CUDA(cudaEventRecord(e0, nullptr));
+  for (int i = 0; i < reps; ++i) PL_CUDA(launch_sgemm_tile(args, sms, nullptr));
+  PL_CUDA(cudaEventRecord(e1, nullptr));
+  PL_CUDA(cudaEventSynchronize(e1));
+  float ms = 0.f;
+  PL_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+  *mean_s = ms * 1e-3 / reps;
+  cudaEventDestroy(e0); cudaEventDestroy(e1);
+  cudaFree(A); cudaFree(B); cudaFree(C); cudaFree(pa); cudaFree(pb);
+  return Runtime::get().check_status(dev);
+}
+
 int PARALiA_bench_link(int dst_loc, int src_loc, int64_t dim, int reps, double* mean_s) {
   if (!mean_s || reps <= 0 || dim <= 0) return fail(PARALIA_ERR_INVALID_ARG, "bad bench arguments");
   Runtime& rt = Runtime::get();

@@ -17,6 +17,7 @@
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
+#include <type_traits>
 #include <vector>
 
 #include "autotune.hpp"
@@ -27,6 +28,8 @@
 #include "group.hpp"
 
 namespace paralia {
+
+int sm_count_of(int dev);   // sgemm_exec.cpp
 
 namespace {
 
@@ -61,7 +64,7 @@ struct UnitState {
   bool a_native_ok = false, b_native_ok = false, c_native = false;
   size_t cursor = 0;                   // next subkernel (ctile index * Kt + ki) to enqueue
   std::vector<cudaEvent_t> exec_tail;  // last event per exec stream
-  cudaEvent_t h2d_tail = nullptr, p2p_tail = nullptr;
+  cudaEvent_t h2d_tail = nullptr, p2p_tail = nullptr, pack_tail = nullptr;
 };
 
 template <typename T>
@@ -93,7 +96,13 @@ struct GemmCall {
   int64_t mrows(int64_t mi) const { return std::min(Tt, M - mi * Tt); }
   int64_t ncols(int64_t ni) const { return std::min(Tt, N - ni * Tt); }
   int64_t klen(int64_t ki) const { return std::min(Tt, K - ki * Tt); }
-  size_t block_bytes() const { return (size_t)TL * TL * esz; }
+  // A cache block holds one FP64 tile, or one packed FP32 operand tile (hi and lo planes,
+  // rows padded to the MMA's N) -- which is also large enough for an FP32 C tile.
+  size_t block_bytes() const {
+    if (std::is_same<T, float>::value)
+      return (size_t)2 * round_up(Tt, SG_BN) * round_up(Tt, SG_BK) * 4;
+    return (size_t)TL * TL * esz;
+  }
   char* block_ptr(const UnitState& u, int blk) const {
     return static_cast<char*>(Runtime::get().dev(u.dev).slab) + (size_t)blk * block_bytes();
   }
@@ -206,9 +215,126 @@ int copy_tile_in(GemmCall<T>& g, UnitState& u, int blk, const char* src, int64_t
   return PARALIA_OK;
 }
 
+// ---- FP32 operands --------------------------------------------------------------------
+// An FP32 tile is never read in place: the tensor-core kernel wants it split into TF32
+// hi/lo planes in its shared-memory order (sgemm_tile.cuh). A tile therefore goes
+//   user memory on a reachable GPU --pack kernel--> cache block, or
+//   host (or unreachable GPU) --copy--> staging slot --pack kernel--> cache block,
+// and a tile that another GPU has already packed is copied from that GPU's block.
+template <typename T>
+int pack_into_block(GemmCall<T>& g, UnitState& u, Resident& r, const OperandDesc& op,
+                    const TileGeom<T>& t, int rows, int klen, int rb, cudaEvent_t also_record) {
+  Runtime& rt = Runtime::get();
+  DeviceCtx& dc = rt.dev(u.dev);
+  void* dst = g.block_ptr(u, r.block);
+  const bool reachable = op.loc >= 0 && (op.loc == u.dev || rt.peer_ok(u.dev, op.loc));
+  if (reachable) {
+    PL_CUDA(launch_sgemm_pack((const float*)t.src, op.ld, t.k_is_row, rows, klen, rb, dst, dc.pack));
+    if (op.loc == u.dev) g.rep->d2d_bytes += (int64_t)rows * klen * 4;
+    else g.rep->p2p_bytes += (int64_t)rows * klen * 4;
+  } else {
+    const int slot = dc.stage_next;
+    dc.stage_next = (dc.stage_next + 1) % DeviceCtx::STAGE_SLOTS;
+    char* stage = static_cast<char*>(dc.stage) + (size_t)slot * dc.stage_slot_bytes;
+    cudaStream_t cs = op.loc == -1 ? dc.h2d : dc.p2p;
+    if (dc.stage_used[slot]) PL_CUDA(cudaStreamWaitEvent(cs, dc.stage_free[slot], 0));
+    PL_CUDA(cudaMemcpy2DAsync(stage, t.nr * 4, t.src, op.ld * 4, t.nr * 4, t.nc, cudaMemcpyDefault, cs));
+    cudaEvent_t landed;
+    PL_TRY(rt.get_event(u.dev, &landed));
+    PL_CUDA(cudaEventRecord(landed, cs));
+    if (op.loc == -1) { g.rep->h2d_bytes += t.nr * t.nc * 4; u.h2d_tail = landed; }
+    else { g.rep->p2p_bytes += t.nr * t.nc * 4; u.p2p_tail = landed; }
+    PL_CUDA(cudaStreamWaitEvent(dc.pack, landed, 0));
+    PL_CUDA(launch_sgemm_pack((const float*)stage, t.nr, t.k_is_row, rows, klen, rb, dst, dc.pack));
+    PL_CUDA(cudaEventRecord(dc.stage_free[slot], dc.pack));
+    dc.stage_used[slot] = true;
+  }
+  g.rep->kernel_launches += 1;
+  PL_CUDA(cudaEventRecord(r.ready, dc.pack));
+  if (also_record) PL_CUDA(cudaEventRecord(also_record, dc.pack));
+  u.pack_tail = r.ready;
+  return PARALIA_OK;
+}
+
+template <typename T>
+int ensure_input(GemmCall<T>& g, int ui, bool is_a, int64_t i0, int64_t i1);
+
+template <typename T>
+int ensure_input_f32(GemmCall<T>& g, int ui, bool is_a, int64_t i0, int64_t i1) {
+  Runtime& rt = Runtime::get();
+  UnitState& u = g.units[ui];
+  const OperandDesc& op = is_a ? g.A : g.B;
+  const int64_t tid = is_a ? i0 * g.Kt + i1 : i0 * g.Nt + i1;
+  Resident& r = is_a ? u.a[tid] : u.b[tid];
+  if (r.present) return PARALIA_OK;
+  const TileGeom<T> t = is_a ? geom_a(g, i0, i1) : geom_b(g, i0, i1);
+  const int rows = (int)(is_a ? g.mrows(i0) : g.ncols(i1));
+  const int klen = (int)(is_a ? g.klen(i1) : g.klen(i0));
+  const int rb = is_a ? SG_BM : SG_BN;
+  const size_t packed = sgemm_packed_bytes(rows, klen, rb);
+  PL_CUDA(cudaSetDevice(u.dev));
+  DeviceCtx& dc = rt.dev(u.dev);
+  if (g.grp && op.loc == -1 && (is_a ? g.share_a : g.share_b)) {
+    int d1, d2;
+    g.grp->grid(&d1, &d2);
+    const int me = g.grp->rank(), gr = me / d2, gc = me % d2;
+    const int slot = is_a ? (int)tid : g.nA + (int)tid;
+    const int home = is_a ? gr * d2 + (int)((i0 + i1) % d2) : (int)((i0 + i1) % d1) * d2 + gc;
+    if (home == me) {
+      r.block = slot;
+      PL_TRY(rt.get_event(u.dev, &r.ready));
+      PL_TRY(pack_into_block(g, u, r, op, t, rows, klen, rb, g.grp->own_event(slot)));
+      r.present = true;
+      return PARALIA_OK;
+    }
+    if (g.prefetch_phase) return PARALIA_OK;
+    r.block = slot;
+    PL_TRY(rt.get_event(u.dev, &r.ready));
+    cudaEvent_t landed;
+    PL_TRY(g.grp->peer_event(home, slot, &landed));
+    PL_CUDA(cudaStreamWaitEvent(dc.p2p, landed, 0));
+    const int peer_slot = is_a ? (int)tid : g.grp->info(home).nA + (int)tid;
+    PL_CUDA(cudaMemcpyAsync(g.block_ptr(u, r.block),
+                            g.grp->peer_slab(home) + (size_t)peer_slot * g.block_bytes(), packed,
+                            cudaMemcpyDefault, dc.p2p));
+    g.rep->p2p_bytes += (int64_t)packed;
+    PL_CUDA(cudaEventRecord(r.ready, dc.p2p));
+    u.p2p_tail = r.ready;
+    r.present = true;
+    return PARALIA_OK;
+  }
+  if (g.grp) r.block = is_a ? (int)tid : g.nA + (int)tid;
+  else PL_TRY(take_block(g, u, &r.block));
+  PL_TRY(rt.get_event(u.dev, &r.ready));
+  int home = ui;
+  if (op.loc == -1 && !g.grp) {
+    const std::vector<int>& cons = is_a ? g.a_consumers[i0] : g.b_consumers[i1];
+    if (g.peer_fetch && cons.size() > 1) home = cons[(size_t)(i0 + i1) % cons.size()];
+    if (home != ui && !rt.peer_ok(u.dev, g.units[home].dev)) home = ui;
+  }
+  if (home == ui) {
+    PL_TRY(pack_into_block(g, u, r, op, t, rows, klen, rb, nullptr));
+  } else {
+    // packed once on the home GPU, copied from its cache block over NVLink
+    PL_TRY(ensure_input(g, home, is_a, i0, i1));
+    PL_CUDA(cudaSetDevice(u.dev));
+    UnitState& h = g.units[home];
+    const Resident& hr = is_a ? h.a[tid] : h.b[tid];
+    PL_CUDA(cudaStreamWaitEvent(dc.p2p, hr.ready, 0));
+    PL_CUDA(cudaMemcpyAsync(g.block_ptr(u, r.block), g.block_ptr(h, hr.block), packed,
+                            cudaMemcpyDefault, dc.p2p));
+    g.rep->p2p_bytes += (int64_t)packed;
+    PL_CUDA(cudaEventRecord(r.ready, dc.p2p));
+    u.p2p_tail = r.ready;
+  }
+  r.present = true;
+  return PARALIA_OK;
+}
+
 // Make a tile of A or B readable on unit `ui`; enqueue whatever copies that takes.
 template <typename T>
 int ensure_input(GemmCall<T>& g, int ui, bool is_a, int64_t i0, int64_t i1) {
+  if (std::is_same<T, float>::value) return ensure_input_f32(g, ui, is_a, i0, i1);
   Runtime& rt = Runtime::get();
   UnitState& u = g.units[ui];
   const OperandDesc& op = is_a ? g.A : g.B;
@@ -326,17 +452,6 @@ int ensure_csrc(GemmCall<T>& g, int ui, int ct) {
   return PARALIA_OK;
 }
 
-template <typename T>
-int launch_tile(const CUtensorMap& mapA, const CUtensorMap& mapB, const DgemmArgs& args,
-                bool a_kc, bool b_kc, cudaStream_t s);
-
-template <>
-int launch_tile<double>(const CUtensorMap& mapA, const CUtensorMap& mapB, const DgemmArgs& args,
-                        bool a_kc, bool b_kc, cudaStream_t s) {
-  PL_CUDA(launch_dgemm_tile(mapA, mapB, args, a_kc, b_kc, s));
-  return PARALIA_OK;
-}
-
 // Copy a finished C tile from its cache block to where C lives, after its last kernel.
 template <typename T>
 int issue_writeback(GemmCall<T>& g, const typename GemmCall<T>::PendingWb& wb) {
@@ -351,13 +466,14 @@ int issue_writeback(GemmCall<T>& g, const typename GemmCall<T>::PendingWb& wb) {
   return PARALIA_OK;
 }
 
+template <typename T> struct TileKernel;
+template <> struct TileKernel<double> { using Args = DgemmArgs; };
+template <> struct TileKernel<float> { using Args = SgemmArgs; };
+
 // Enqueue subkernels [ki0, ki1) of C tile `ct` on unit ui as one launch.
 template <typename T>
-int enqueue_subkernels(GemmCall<T>& g, int ui, int order_idx, int ct, int ki0, int ki1);
-
-template <>
-int enqueue_subkernels<double>(GemmCall<double>& g, int ui, int order_idx, int ct, int ki0,
-                               int ki1) {
+int enqueue_subkernels(GemmCall<T>& g, int ui, int order_idx, int ct, int ki0, int ki1) {
+  constexpr bool IS_F64 = std::is_same<T, double>::value;
   Runtime& rt = Runtime::get();
   UnitState& u = g.units[ui];
   DeviceCtx& dc = rt.dev(u.dev);
@@ -366,7 +482,7 @@ int enqueue_subkernels<double>(GemmCall<double>& g, int ui, int order_idx, int c
   cudaStream_t es = dc.exec[sidx];
   PL_CUDA(cudaSetDevice(u.dev));
 
-  DgemmArgs args;
+  typename TileKernel<T>::Args args;
   memset(&args, 0, sizeof(args));
   args.nparts = 0;
   bool a_native = false, b_native = false;
@@ -376,14 +492,21 @@ int enqueue_subkernels<double>(GemmCall<double>& g, int ui, int order_idx, int c
     PL_CUDA(cudaSetDevice(u.dev));
     const Resident& ra = u.a[mi * g.Kt + ki];
     const Resident& rb = u.b[ki * g.Nt + ni];
-    DgemmKPart& p = args.parts[args.nparts++];
+    auto& p = args.parts[args.nparts++];
     p.klen = (int32_t)g.klen(ki);
     a_native = ra.native;
     b_native = rb.native;
-    if (ra.native) { p.a_m = (int32_t)(mi * g.Tt); p.a_k = (int32_t)(ki * g.Tt); p.a_z = 0; }
-    else { p.a_m = 0; p.a_k = 0; p.a_z = ra.block; PL_CUDA(cudaStreamWaitEvent(es, ra.ready, 0)); }
-    if (rb.native) { p.b_k = (int32_t)(ki * g.Tt); p.b_n = (int32_t)(ni * g.Tt); p.b_z = 0; }
-    else { p.b_k = 0; p.b_n = 0; p.b_z = rb.block; PL_CUDA(cudaStreamWaitEvent(es, rb.ready, 0)); }
+    if (!ra.native) PL_CUDA(cudaStreamWaitEvent(es, ra.ready, 0));
+    if (!rb.native) PL_CUDA(cudaStreamWaitEvent(es, rb.ready, 0));
+    if constexpr (IS_F64) {
+      if (ra.native) { p.a_m = (int32_t)(mi * g.Tt); p.a_k = (int32_t)(ki * g.Tt); p.a_z = 0; }
+      else { p.a_m = 0; p.a_k = 0; p.a_z = ra.block; }
+      if (rb.native) { p.b_k = (int32_t)(ki * g.Tt); p.b_n = (int32_t)(ni * g.Tt); p.b_z = 0; }
+      else { p.b_k = 0; p.b_n = 0; p.b_z = rb.block; }
+    } else {
+      p.a_packed = g.block_ptr(u, ra.block);
+      p.b_packed = g.block_ptr(u, rb.block);
+    }
   }
 
   const bool first = (ki0 == 0), last = (ki1 == g.Kt);
@@ -398,34 +521,39 @@ int enqueue_subkernels<double>(GemmCall<double>& g, int ui, int order_idx, int c
   args.alpha = g.alpha;
   args.status = dc.status_dev;
   args.Csrc = nullptr;
-  args.beta_src = 0.0;
+  args.beta_src = 0;
   if (rc.native) {
     // C lives on this GPU: update it in place, beta on the first k only
     // (the reference switches such tiles to plain WR, dgemm.cpp:262-263).
-    args.C = (double*)g.C.ptr + mi * g.Tt + ni * g.Tt * g.C.ld;
+    args.C = (T*)g.C.ptr + mi * g.Tt + ni * g.Tt * g.C.ld;
     args.ldc = g.C.ld;
-    args.beta_c = first ? g.beta : 1.0;
-    args.vec_ok = tma_addressable(g.C.ptr, g.C.ld, g.esz) ? 1 : 0;
+    args.beta_c = first ? g.beta : (T)1;
+    if constexpr (IS_F64) args.vec_ok = tma_addressable(g.C.ptr, g.C.ld, g.esz) ? 1 : 0;
   } else {
-    args.C = (double*)g.block_ptr(u, rc.block);
+    args.C = (T*)g.block_ptr(u, rc.block);
     args.ldc = g.TL;
-    args.beta_c = first ? 0.0 : 1.0;   // WR_LAZY: accumulate from zero (dgemm.cpp:273-279)
-    args.vec_ok = 1;
-    if (g.beta != 0.0) {
+    args.beta_c = first ? (T)0 : (T)1;   // WR_LAZY: accumulate from zero (dgemm.cpp:273-279)
+    if constexpr (IS_F64) args.vec_ok = 1;
+    if (g.beta != (T)0) {
       Resident& rs = u.csrc[ct];
       if (first) PL_TRY(ensure_csrc(g, ui, ct));
       if (last) {
         PL_CUDA(cudaStreamWaitEvent(es, rs.ready, 0));
-        args.Csrc = (const double*)g.block_ptr(u, rs.block);
+        args.Csrc = (const T*)g.block_ptr(u, rs.block);
         args.ldcsrc = g.TL;
         args.beta_src = g.beta;
       }
     }
   }
-  const bool a_kc = g.A.trans, b_kc = !g.B.trans;
-  const CUtensorMap& mapA = a_native ? u.map_a_native : (a_kc ? u.map_slab_kc : u.map_slab_mn);
-  const CUtensorMap& mapB = b_native ? u.map_b_native : (b_kc ? u.map_slab_kc : u.map_slab_mn);
-  PL_TRY(launch_tile<double>(mapA, mapB, args, a_kc, b_kc, es));
+  if constexpr (IS_F64) {
+    const bool a_kc = g.A.trans, b_kc = !g.B.trans;
+    const CUtensorMap& mapA = a_native ? u.map_a_native : (a_kc ? u.map_slab_kc : u.map_slab_mn);
+    const CUtensorMap& mapB = b_native ? u.map_b_native : (b_kc ? u.map_slab_kc : u.map_slab_mn);
+    PL_CUDA(launch_dgemm_tile(mapA, mapB, args, a_kc, b_kc, es));
+  } else {
+    (void)a_native; (void)b_native;
+    PL_CUDA(launch_sgemm_tile(args, sm_count_of(u.dev), es));
+  }
   g.rep->kernel_launches += 1;
 
   cudaEvent_t done;
@@ -435,8 +563,8 @@ int enqueue_subkernels<double>(GemmCall<double>& g, int ui, int order_idx, int c
   if (last && !rc.native) {
     // Write the finished tile back to where C lives (reference: WBTileMap, dgemm.cpp:583).
     char* dst = (char*)g.C.ptr + (mi * g.Tt + ni * g.Tt * g.C.ld) * g.esz;
-    typename GemmCall<double>::PendingWb wb{ui, done, dst, g.C.ld, g.block_ptr(u, rc.block),
-                                           (int64_t)args.M, (int64_t)args.N};
+    typename GemmCall<T>::PendingWb wb{ui, done, dst, g.C.ld, g.block_ptr(u, rc.block),
+                                      (int64_t)args.M, (int64_t)args.N};
     if (g.defer_wb && g.C.loc == -1) g.pending_wb.push_back(wb);
     else PL_TRY(issue_writeback(g, wb));
   }
@@ -604,8 +732,10 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
     u.c.assign(g.Mt * g.Nt, Resident());
     u.csrc.assign(g.Mt * g.Nt, Resident());
     u.exec_tail.assign(g.exec_streams, nullptr);
-    u.a_native_ok = g.A.loc == u.dev && tma_addressable(g.A.ptr, g.A.ld, g.esz);
-    u.b_native_ok = g.B.loc == u.dev && tma_addressable(g.B.ptr, g.B.ld, g.esz);
+    // FP32 tiles are always packed into cache blocks, never read in place
+    const bool in_place_ok = std::is_same<T, double>::value;
+    u.a_native_ok = in_place_ok && g.A.loc == u.dev && tma_addressable(g.A.ptr, g.A.ld, g.esz);
+    u.b_native_ok = in_place_ok && g.B.loc == u.dev && tma_addressable(g.B.ptr, g.B.ld, g.esz);
     u.c_native = g.C.loc == u.dev;
     // Blocks this unit needs if nothing is ever evicted: the A tile rows and B tile
     // columns of its C tiles, plus accumulator (and original-C) blocks
@@ -647,12 +777,18 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
       rc = rt.ensure_slab(u.dev, bytes, &alloc_ms);
       if (rc != PARALIA_OK) return fail_out(rc);
       DeviceCtx& dc = rt.dev(u.dev);
-      const uint64_t nb = dc.slab_bytes / g.block_bytes();
-      rc = make_tensor_map(&u.map_slab_kc, dc.slab, g.esz, g.TL, g.TL, nb, g.TL * g.esz,
-                           g.block_bytes(), 16, 128);
-      if (rc == PARALIA_OK)
-        rc = make_tensor_map(&u.map_slab_mn, dc.slab, g.esz, g.TL, g.TL, nb, g.TL * g.esz,
-                             g.block_bytes(), 16, 16);
+      if (std::is_same<T, double>::value) {
+        const uint64_t nb = dc.slab_bytes / g.block_bytes();
+        rc = make_tensor_map(&u.map_slab_kc, dc.slab, g.esz, g.TL, g.TL, nb, g.TL * g.esz,
+                             g.block_bytes(), 16, 128);
+        if (rc == PARALIA_OK)
+          rc = make_tensor_map(&u.map_slab_mn, dc.slab, g.esz, g.TL, g.TL, nb, g.TL * g.esz,
+                               g.block_bytes(), 16, 16);
+        if (rc != PARALIA_OK) return fail_out(rc);
+      }
+    }
+    if (std::is_same<T, float>::value && K > 0) {
+      rc = rt.ensure_stage(u.dev, (size_t)g.Tt * g.Tt * g.esz);
       if (rc != PARALIA_OK) return fail_out(rc);
     }
     if (u.a_native_ok && K > 0) {
@@ -678,6 +814,7 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
     // Nothing of this call may start before the start event.
     for (int s = 0; s < g.exec_streams; ++s) cudaStreamWaitEvent(dc.exec[s], dc.t_begin, 0);
     cudaStreamWaitEvent(dc.p2p, dc.t_begin, 0);
+    cudaStreamWaitEvent(dc.pack, dc.t_begin, 0);
     cudaStreamWaitEvent(dc.d2h, dc.t_begin, 0);
   }
   // With four or more GPUs pulling from the host at once, this class of host delivers far
@@ -760,6 +897,7 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
         if (u.exec_tail[s]) cudaStreamWaitEvent(dc.d2h, u.exec_tail[s], 0);
       if (u.h2d_tail) cudaStreamWaitEvent(dc.d2h, u.h2d_tail, 0);
       if (u.p2p_tail) cudaStreamWaitEvent(dc.d2h, u.p2p_tail, 0);
+      if (u.pack_tail) cudaStreamWaitEvent(dc.d2h, u.pack_tail, 0);
       cudaEventRecord(dc.t_end, dc.d2h);
     }
   }
@@ -797,6 +935,13 @@ int exec_dgemm(char ta, char tb, int64_t M, int64_t N, int64_t K, double alpha, 
                double* C, int64_t ldC, int locC, const paralia_ctl* ctl, paralia_report* out) {
   return run_gemm<double>(ta, tb, M, N, K, alpha, A, ldA, locA, B, ldB, locB, beta, C, ldC, locC,
                           ctl, out, "Dgemm");
+}
+
+int exec_sgemm(char ta, char tb, int64_t M, int64_t N, int64_t K, float alpha, const float* A,
+               int64_t ldA, int locA, const float* B, int64_t ldB, int locB, float beta, float* C,
+               int64_t ldC, int locC, const paralia_ctl* ctl, paralia_report* out) {
+  return run_gemm<float>(ta, tb, M, N, K, alpha, A, ldA, locA, B, ldB, locB, beta, C, ldC, locC,
+                         ctl, out, "Sgemm");
 }
 
 int exec_group_dgemm(char ta, char tb, int64_t M, int64_t N, int64_t K, double alpha,

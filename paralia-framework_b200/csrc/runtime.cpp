@@ -60,12 +60,24 @@ int Runtime::ensure_device(int d) {
   PL_CUDA(cudaStreamCreateWithFlags(&c.p2p, cudaStreamNonBlocking));
   for (int i = 0; i < MAX_EXEC_STREAMS; ++i)
     PL_CUDA(cudaStreamCreateWithFlags(&c.exec[i], cudaStreamNonBlocking));
+  PL_CUDA(cudaStreamCreateWithFlags(&c.pack, cudaStreamNonBlocking));
+  for (int i = 0; i < DeviceCtx::STAGE_SLOTS; ++i)
+    PL_CUDA(cudaEventCreateWithFlags(&c.stage_free[i], cudaEventDisableTiming));
   PL_CUDA(cudaEventCreate(&c.t_begin));
   PL_CUDA(cudaEventCreate(&c.t_end));
   PL_CUDA(cudaMalloc(&c.status_dev, sizeof(int)));
   PL_CUDA(cudaMemset(c.status_dev, 0, sizeof(int)));
   PL_CUDA(dgemm_tile_configure());
   PL_CUDA(sgemm_tile_configure());
+  {
+    // keep stream-ordered scratch (per-tile SGEMM packing) cached between calls
+    cudaMemPool_t pool;
+    if (cudaDeviceGetDefaultMemPool(&pool, d) == cudaSuccess) {
+      uint64_t keep = UINT64_MAX;
+      cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+    }
+    cudaGetLastError();
+  }
   // Peer access between this GPU and every GPU already in use (reference: CoCoEnableLinks
   // for every location, dgemm.cpp:423). Done pairwise as GPUs come into use, so a process
   // that drives a single GPU never creates a context on the others. On an NVSwitch box
@@ -144,6 +156,28 @@ int Runtime::ensure_dot_scratch(int d, size_t partials_n, size_t results_n) {
   return PARALIA_OK;
 }
 
+int Runtime::ensure_stage(int d, size_t slot_bytes) {
+  DeviceCtx& c = devs_[d];
+  if (c.stage_slot_bytes >= slot_bytes) return PARALIA_OK;
+  PL_CUDA(cudaSetDevice(d));
+  if (c.stage) {
+    PL_CUDA(cudaDeviceSynchronize());
+    PL_CUDA(cudaFree(c.stage));
+    c.stage = nullptr;
+    c.stage_slot_bytes = 0;
+  }
+  cudaError_t e = cudaMalloc(&c.stage, slot_bytes * DeviceCtx::STAGE_SLOTS);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(PARALIA_ERR_OUT_OF_MEMORY, "GPU %d: cannot allocate the staging ring (%s)", d,
+                cudaGetErrorString(e));
+  }
+  c.stage_slot_bytes = slot_bytes;
+  for (int i = 0; i < DeviceCtx::STAGE_SLOTS; ++i) c.stage_used[i] = false;
+  c.stage_next = 0;
+  return PARALIA_OK;
+}
+
 int Runtime::get_event(int d, cudaEvent_t* ev) {
   DeviceCtx& c = devs_[d];
   if (c.events_used == c.event_pool.size()) {
@@ -179,6 +213,7 @@ int Runtime::finalize() {
     if (cudaSetDevice(d) != cudaSuccess) continue;
     cudaDeviceSynchronize();
     if (c.slab) cudaFree(c.slab);
+    if (c.stage) cudaFree(c.stage);
     if (c.status_dev) cudaFree(c.status_dev);
     if (c.dot_partials) cudaFree(c.dot_partials);
     if (c.dot_results) cudaFree(c.dot_results);
@@ -188,6 +223,8 @@ int Runtime::finalize() {
       cudaStreamDestroy(c.h2d);
       cudaStreamDestroy(c.d2h);
       cudaStreamDestroy(c.p2p);
+      cudaStreamDestroy(c.pack);
+      for (int i = 0; i < DeviceCtx::STAGE_SLOTS; ++i) cudaEventDestroy(c.stage_free[i]);
       for (int i = 0; i < MAX_EXEC_STREAMS; ++i) cudaStreamDestroy(c.exec[i]);
       cudaEventDestroy(c.t_begin);
       cudaEventDestroy(c.t_end);

@@ -44,6 +44,14 @@ struct DeviceCtx {
   cudaStream_t d2h = nullptr;   // this GPU -> host (or owner GPU) write-backs
   cudaStream_t p2p = nullptr;   // peer GPU -> this GPU tile fetches
   cudaStream_t exec[MAX_EXEC_STREAMS] = {};
+  cudaStream_t pack = nullptr;  // FP32 operand packing (hi/lo split) kernels
+  // Ring of raw-tile staging buffers between a host/peer copy and its pack kernel.
+  static constexpr int STAGE_SLOTS = 4;
+  void* stage = nullptr;
+  size_t stage_slot_bytes = 0;
+  cudaEvent_t stage_free[STAGE_SLOTS] = {};   // slot may be overwritten after this
+  bool stage_used[STAGE_SLOTS] = {};
+  int stage_next = 0;
   cudaEvent_t t_begin = nullptr, t_end = nullptr;  // timing events
   // Tile cache: one allocation cut into equal blocks (reference: Buffer / CBlock,
   // sized by ManageCachesDgemm, Library_scheduler/src/Functions/dgemm.cpp:23-121).
@@ -76,6 +84,8 @@ class Runtime {
   int ensure_slab(int d, size_t bytes, double* alloc_ms);
   int free_slab(int d);
   int ensure_dot_scratch(int d, size_t partials_n, size_t results_n);
+  // Staging ring of GPU d with slots of at least `slot_bytes`.
+  int ensure_stage(int d, size_t slot_bytes);
   // Borrow an event (timing disabled) from GPU d's pool; valid until release_events(d).
   int get_event(int d, cudaEvent_t* ev);
   void release_events(int d) { devs_[d].events_used = 0; }

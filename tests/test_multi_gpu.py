@@ -120,6 +120,21 @@ def test_level1_two_gpus(pl, orc):
     assert np.array_equal(y, want_y)
 
 
+@need2
+def test_sgemm_two_gpus(pl, orc):
+    M, N, K, T = 1024, 768, 512, 256
+    A = orc.uniform_f32(M * K, 42).reshape((M, K), order="F")
+    B = orc.uniform_f32(K * N, 43).reshape((K, N), order="F")
+    C = orc.uniform_f32(M * N, 44).reshape((M, N), order="F")
+    want = 1.25 * (A.astype(np.float64) @ B.astype(np.float64)) + 0.75 * C.astype(np.float64)
+    C1 = C.copy(order="F")
+    pl.sgemm("N", "N", M, N, K, 1.25, A, M, B, K, 0.75, C1, M, ctl=pl.make_ctl(T=T, units=[0]))
+    rep = pl.sgemm("N", "N", M, N, K, 1.25, A, M, B, K, 0.75, C, M, ctl=pl.make_ctl(T=T, units=[0, 1]))
+    assert orc.normwise_rel_err(C, want) <= 4 * K * 2.0 ** -23
+    assert np.array_equal(C, C1)          # same bits on one and on two GPUs
+    assert rep.h2d_bytes == (M * K + K * N + M * N) * 4 and rep.p2p_bytes > 0
+
+
 @need4
 def test_dgemm_four_gpus_grid(pl, orc):
     M, N, K, T = 1024, 1024, 512, 256
