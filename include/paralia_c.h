@@ -244,6 +244,11 @@ int PARALiA_bench_tile_sgemm(int dev, int64_t T, int reps, double* mean_s);
 /* Time a strided 2-D tile copy dim x dim doubles src_loc -> dst_loc; mean seconds. */
 int PARALiA_bench_link(int dst_loc, int src_loc, int64_t dim, int reps, double* mean_s);
 
+/* The same copy alone and while ten times as many copies keep link (odst <- osrc) busy
+ * (reference: transfer_link_microbench.cu:186-218); slowdown = t_shared / t_alone. */
+int PARALiA_bench_link_overlap(int dst_loc, int src_loc, int odst_loc, int osrc_loc, int64_t dim,
+                               int reps, double* t_alone, double* t_shared);
+
 #ifdef __cplusplus
 }
 #endif

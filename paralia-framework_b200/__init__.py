@@ -149,6 +149,8 @@ SIGNATURES = {
     "PARALiA_bench_tile_dgemm": (C.c_int, [C.c_int, _chr, _chr, _i64, C.c_int, C.POINTER(_dbl)]),
     "PARALiA_bench_tile_sgemm": (C.c_int, [C.c_int, _i64, C.c_int, C.POINTER(_dbl)]),
     "PARALiA_bench_link": (C.c_int, [C.c_int, C.c_int, _i64, C.c_int, C.POINTER(_dbl)]),
+    "PARALiA_bench_link_overlap": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, _i64, C.c_int,
+                                             C.POINTER(_dbl), C.POINTER(_dbl)]),
 }
 
 _lib = None
@@ -399,3 +401,11 @@ def bench_link(dst_loc, src_loc, dim, reps) -> float:
     v = C.c_double()
     _check(lib().PARALiA_bench_link(dst_loc, src_loc, dim, reps, C.byref(v)))
     return v.value
+
+
+def bench_link_overlap(dst_loc, src_loc, odst_loc, osrc_loc, dim, reps):
+    """(t_alone, t_shared) of link dst<-src while link odst<-osrc is kept busy."""
+    a, b = C.c_double(), C.c_double()
+    _check(lib().PARALiA_bench_link_overlap(dst_loc, src_loc, odst_loc, osrc_loc, dim, reps,
+                                            C.byref(a), C.byref(b)))
+    return a.value, b.value

@@ -475,6 +475,7 @@ int PARALiA_bench_link(int dst_loc, int src_loc, int64_t dim, int reps, double* 
   if (rc != PARALIA_OK) { PARALiA_free(src, src_loc); return rc; }
   const int drive = dst_loc >= 0 ? dst_loc : src_loc;
   rc = rt.ensure_device(drive);
+  if (rc == PARALIA_OK && dst_loc >= 0 && src_loc >= 0) rc = rt.ensure_device(src_loc);  // peer access
   if (rc == PARALIA_OK) {
     cudaSetDevice(drive);
     cudaStream_t s = dst_loc >= 0 ? (src_loc >= 0 ? rt.dev(drive).p2p : rt.dev(drive).h2d)
@@ -497,6 +498,71 @@ int PARALiA_bench_link(int dst_loc, int src_loc, int64_t dim, int reps, double* 
   }
   PARALiA_free(src, src_loc);
   PARALiA_free(dst, dst_loc);
+  return rc;
+}
+
+// Time a dim x dim tile copy on link (dst <- src) alone and while `background` copies of
+// the same size keep link (odst <- osrc) busy: the reference's link-sharing measurement
+// (Database_builder/CuCuBLAS/src/transfer_link_microbench.cu:186-218).
+int PARALiA_bench_link_overlap(int dst_loc, int src_loc, int odst_loc, int osrc_loc, int64_t dim,
+                               int reps, double* t_alone, double* t_shared) {
+  if (!t_alone || !t_shared || reps <= 0 || dim <= 0)
+    return fail(PARALIA_ERR_INVALID_ARG, "bad bench arguments");
+  if (dst_loc == src_loc || odst_loc == osrc_loc)
+    return fail(PARALIA_ERR_INVALID_ARG, "source and destination are the same");
+  Runtime& rt = Runtime::get();
+  PL_TRY(rt.init());
+  DeviceGuard guard;
+  const int64_t bytes = dim * dim * 8;
+  void *s1 = nullptr, *d1 = nullptr, *s2 = nullptr, *d2 = nullptr;
+  int rc = PARALiA_malloc(&s1, bytes, src_loc);
+  if (rc == PARALIA_OK) rc = PARALiA_malloc(&d1, bytes, dst_loc);
+  if (rc == PARALIA_OK) rc = PARALiA_malloc(&s2, bytes, osrc_loc);
+  if (rc == PARALIA_OK) rc = PARALiA_malloc(&d2, bytes, odst_loc);
+  const int drv1 = dst_loc >= 0 ? dst_loc : src_loc, drv2 = odst_loc >= 0 ? odst_loc : osrc_loc;
+  for (int l : {dst_loc, src_loc, odst_loc, osrc_loc})
+    if (rc == PARALIA_OK && l >= 0) rc = rt.ensure_device(l);
+  if (rc == PARALIA_OK) {
+    auto pick = [&](int dst, int src, int drv) {
+      DeviceCtx& c = rt.dev(drv);
+      return dst >= 0 ? (src >= 0 ? c.p2p : c.h2d) : c.d2h;
+    };
+    cudaStream_t q1 = pick(dst_loc, src_loc, drv1), q2 = pick(odst_loc, osrc_loc, drv2);
+    if (q1 == q2) q2 = rt.dev(drv2).exec[0];
+    cudaEvent_t e0, e1;
+    cudaSetDevice(drv1);
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    auto timed = [&](bool with_bg, double* out) {
+      cudaSetDevice(drv1);
+      cudaMemcpyAsync(d1, s1, bytes, cudaMemcpyDefault, q1);   // warm-up
+      cudaStreamSynchronize(q1);
+      if (with_bg) {
+        cudaSetDevice(drv2);
+        for (int i = 0; i < 10 * reps; ++i) cudaMemcpyAsync(d2, s2, bytes, cudaMemcpyDefault, q2);
+      }
+      cudaSetDevice(drv1);
+      cudaEventRecord(e0, q1);
+      for (int i = 0; i < reps; ++i) cudaMemcpyAsync(d1, s1, bytes, cudaMemcpyDefault, q1);
+      cudaEventRecord(e1, q1);
+      cudaEventSynchronize(e1);
+      float ms = 0.f;
+      cudaEventElapsedTime(&ms, e0, e1);
+      *out = ms * 1e-3 / reps;
+      cudaSetDevice(drv2);
+      cudaStreamSynchronize(q2);
+    };
+    timed(false, t_alone);
+    timed(true, t_shared);
+    cudaSetDevice(drv1);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    if (cudaGetLastError() != cudaSuccess) rc = fail(PARALIA_ERR_CUDA, "link overlap benchmark failed");
+  }
+  if (s1) PARALiA_free(s1, src_loc);
+  if (d1) PARALiA_free(d1, dst_loc);
+  if (s2) PARALiA_free(s2, osrc_loc);
+  if (d2) PARALiA_free(d2, odst_loc);
   return rc;
 }
 

@@ -126,3 +126,49 @@ def test_missing_library_fails_loudly(pl, monkeypatch, tmp_path):
     monkeypatch.setattr(pl, "LIB_PATH", tmp_path / "absent.so")
     with pytest.raises(pl.LibraryMissing):
         pl.lib()
+
+
+def test_database_round_trip(pl, tmp_path):
+    """Files in the reference's processed formats (GPUexec_lookup.cpp:79-81,
+    CoModel.cpp:26-38) drive the model: exec time from the lookup table, link time from
+    intercept + coefficient * bytes."""
+    proc = tmp_path / "Processed"
+    proc.mkdir()
+    rate = 30e12
+    rows = "".join(f"N,N,{T},{T},{T},{2.0 * T ** 3 / rate:e},0,0,0,10,1\n" for T in (1024, 2048, 4096))
+    (proc / "Dgemm_lookup-table_dev-0.log").write_text(rows)
+    for g in range(8):
+        for (d, s) in ((g, -1), (-1, g)):
+            (proc / f"Link-Stats_loc_dest-{d}_loc_src-{s}.log").write_text(
+                "Intercept: 1.000000e-05\nCoefficient: 2.000000e-11\nSlowdown([0]->[1]): 1.000000e+00\n")
+    pl.load_database(str(tmp_path))
+    try:
+        rep = pl.autotune_gemm(8, "N", "N", 32768, 32768, 32768, -1, -1, -1,
+                               pl.make_ctl(units=list(range(8))))
+        assert rep.T == 2048
+        t_exec = (32768 / 2048) ** 3 * (2.0 * 2048 ** 3 / rate) / 8
+        t_recv = 3 * (1e-5 + 2e-11 * 32768 * 32768 * 8 / 8)
+        assert t_exec > t_recv
+        assert rep.pred_t == pytest.approx(t_exec * (1 + rep.T_slowdowns[0]), rel=1e-5)
+        # a slow host link makes the same problem link-bound
+        for g in range(8):
+            (proc / f"Link-Stats_loc_dest-{g}_loc_src--1.log").write_text(
+                "Intercept: 1.000000e-05\nCoefficient: 1.000000e-09\n")
+        pl.load_database(str(tmp_path))
+        rep2 = pl.autotune_gemm(8, "N", "N", 32768, 32768, 32768, -1, -1, -1,
+                                pl.make_ctl(units=list(range(8))))
+        t_recv2 = 3 * (1e-5 + 1e-9 * 32768 * 32768 * 8 / 8)
+        assert rep2.pred_t == pytest.approx(t_recv2 * (1 + rep2.T_slowdowns[0]), rel=1e-5)
+    finally:
+        with pytest.raises(pl.ParaliaError):
+            pl.load_database(str(tmp_path / "nowhere"))   # DB missing -> status, state kept
+
+
+def test_runner_mask_parsing(pl):
+    import importlib
+    runner = importlib.import_module("paralia_framework_b200.runner")
+    assert runner.parse_mask(2, "0101") == [0, 2]        # the reference's example
+    assert runner.parse_mask(-1, "0") is None
+    assert runner.parse_mask(8, "11111111") == list(range(8))
+    with pytest.raises(SystemExit):
+        runner.parse_mask(2, "0111")
