@@ -3,8 +3,8 @@
 //
 // It stands where the reference calls cublasSgemm through backend_run_operation
 // (Library_scheduler/src/Functions/sgemm.cpp:85-139). Each FP32 value x is written as
-// hi + lo with hi = x with its low 13 mantissa bits cleared and lo = (x - hi) with its low
-// 13 bits cleared; both are exact TF32 numbers and x - hi - lo is below 2^-21 |x|. The
+// hi + lo with hi = x rounded to the nearest TF32 number and lo = (x - hi) rounded to the
+// nearest TF32 number; both are exact TF32 values and |x - hi - lo| <= 2^-22 |x|. The
 // kernel accumulates lo*hi + hi*lo + hi*hi in FP32, which keeps the normwise error of the
 // product far inside the 4*K*eps32 budget that a plain FP32 GEMM is allowed.
 //
