@@ -62,7 +62,10 @@ struct UnitState {
   CUtensorMap map_slab_kc, map_slab_mn;   // tile cache seen k-contiguous / row-contiguous
   CUtensorMap map_a_native, map_b_native; // user matrices on this GPU
   bool a_native_ok = false, b_native_ok = false, c_native = false;
-  size_t cursor = 0;                   // next subkernel (ctile index * Kt + ki) to enqueue
+  // Launches of this unit in enqueue order: (index into ctiles, first k tile, end k tile).
+  struct Item { int order_idx, ki0, ki1; };
+  std::vector<Item> items;
+  size_t cursor = 0;                   // next item to enqueue
   std::vector<cudaEvent_t> exec_tail;  // last event per exec stream
   cudaEvent_t h2d_tail = nullptr, p2p_tail = nullptr, pack_tail = nullptr;
 };
@@ -536,7 +539,7 @@ int enqueue_subkernels(GemmCall<T>& g, int ui, int order_idx, int ct, int ki0, i
     if constexpr (IS_F64) args.vec_ok = 1;
     if (g.beta != (T)0) {
       Resident& rs = u.csrc[ct];
-      if (first) PL_TRY(ensure_csrc(g, ui, ct));
+      if (csrc_due(g, ki1)) PL_TRY(ensure_csrc(g, ui, ct));
       if (last) {
         PL_CUDA(cudaStreamWaitEvent(es, rs.ready, 0));
         args.Csrc = (const T*)g.block_ptr(u, rs.block);
@@ -590,6 +593,47 @@ int kchain_len(const GemmCall<T>& g, int ki0) {
   int len = forced > 0 ? forced : (ki0 == 0 ? 1 : 4);
   len = std::min<int>(len, DG_MAX_PARTS);
   return std::max(len, 1);
+}
+
+// The original C tile is needed only by the last launch of its C tile: it is fetched when
+// the launch before that one is enqueued (or with the only launch), so that it rides the
+// host link behind the A/B tiles that are needed sooner.
+template <typename T>
+bool csrc_due(const GemmCall<T>& g, int ki1) {
+  return ki1 >= (int)g.Kt - 4;
+}
+
+// Order of a unit's launches. C tiles are taken in bands (consecutive tiles of the unit's
+// distribution order); inside a band all tiles advance through k together: the first k tile
+// of every C tile of the band, then the next chain of k tiles of every C tile, and so on.
+// A fetched A or B tile is thus used by a whole band row or column of launches straight
+// away, which matters while the host link is the bottleneck at start-up; finished bands
+// write back while the next band computes. The k split of each C tile is untouched, so
+// the arithmetic -- and every bit of the result -- is the same as in tile-major order.
+template <typename T>
+void build_items(const GemmCall<T>& g, UnitState& u) {
+  static const int band_env = [] {
+    const char* e = getenv("PARALIA_BAND");
+    return e ? atoi(e) : 0;
+  }();
+  const int n = (int)u.ctiles.size();
+  const int kt = (int)std::max<int64_t>(g.Kt, 1);
+  // about four bands per unit, between 4 and 16 C tiles each (measured best at 4 GPUs)
+  int band = band_env > 0 ? band_env : std::min(16, std::max(4, (n + 3) / 4));
+  u.items.clear();
+  for (int b0 = 0; b0 < n; b0 += band) {
+    const int b1 = std::min(n, b0 + band);
+    if (g.Kt == 0) {
+      for (int oi = b0; oi < b1; ++oi) u.items.push_back({oi, 0, 0});
+      continue;
+    }
+    for (int ki0 = 0; ki0 < kt;) {
+      const int ki1 = std::min(kt, ki0 + kchain_len(g, ki0));
+      for (int oi = b0; oi < b1; ++oi) u.items.push_back({oi, ki0, ki1});
+      ki0 = ki1;
+    }
+  }
+  u.cursor = 0;
 }
 
 template <typename T>
@@ -817,6 +861,7 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
     cudaStreamWaitEvent(dc.pack, dc.t_begin, 0);
     cudaStreamWaitEvent(dc.d2h, dc.t_begin, 0);
   }
+  for (int ui = 0; ui < active; ++ui) build_items(g, g.units[ui]);
   // With four or more GPUs pulling from the host at once, this class of host delivers far
   // less in both directions together than in one direction alone (measured on an
   // 8 x B200 box: 185 GB/s host->GPU alone, 63 + 63 GB/s with GPU->host traffic running),
@@ -826,7 +871,6 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
     const char* e = getenv("PARALIA_DEFER_WB");
     g.defer_wb = e ? atoi(e) != 0 : (grp ? grp->world() : active) >= 4;
   }
-  const int kt_loop = (int)std::max<int64_t>(g.Kt, 1);
   if (grp) {
     // Group mode, phase 1: enqueue the host fetches of the tiles this rank is the home of
     // (in the order its own kernels will want them) and record their inter-process
@@ -834,15 +878,16 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
     if ((g.share_a || g.share_b) && g.Kt > 0) {
       g.prefetch_phase = true;
       UnitState& u = g.units[0];
-      for (size_t oi = 0; oi < u.ctiles.size() && rc == PARALIA_OK; ++oi) {
-        const int64_t mi = u.ctiles[oi] / g.Nt, ni = u.ctiles[oi] % g.Nt;
-        for (int64_t ki = 0; ki < g.Kt && rc == PARALIA_OK; ++ki) {
+      for (size_t it = 0; it < u.items.size() && rc == PARALIA_OK; ++it) {
+        const UnitState::Item item = u.items[it];
+        const int ct = u.ctiles[item.order_idx];
+        const int64_t mi = ct / g.Nt, ni = ct % g.Nt;
+        for (int64_t ki = item.ki0; ki < item.ki1 && rc == PARALIA_OK; ++ki) {
           rc = ensure_input(g, 0, true, mi, ki);
           if (rc == PARALIA_OK) rc = ensure_input(g, 0, false, ki, ni);
-          // keep the host link's queue in the order of use: the original C tile rides
-          // behind the first k's inputs, exactly as in the single-process order
-          if (rc == PARALIA_OK && ki == 0) rc = ensure_csrc(g, 0, u.ctiles[oi]);
         }
+        // keep the host link's queue in the order of use (same rule as the launch path)
+        if (rc == PARALIA_OK && csrc_due(g, item.ki1)) rc = ensure_csrc(g, 0, ct);
       }
       g.prefetch_phase = false;
     }
@@ -856,20 +901,12 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
     work_left = false;
     for (int ui = 0; ui < active; ++ui) {
       UnitState& u = g.units[ui];
-      const size_t total = u.ctiles.size() * (size_t)kt_loop;
-      if (u.cursor >= total) continue;
-      const int order_idx = (int)(u.cursor / kt_loop);
-      const int ki0 = (int)(u.cursor % kt_loop);
-      int ki1 = g.Kt == 0 ? 0 : std::min<int>(kt_loop, ki0 + kchain_len(g, ki0));
-      if (g.Kt == 0) {
-        rc = enqueue_subkernels<T>(g, ui, order_idx, u.ctiles[order_idx], 0, 0);
-        u.cursor = (size_t)(order_idx + 1) * kt_loop;
-      } else {
-        rc = enqueue_subkernels<T>(g, ui, order_idx, u.ctiles[order_idx], ki0, ki1);
-        u.cursor += (size_t)(ki1 - ki0);
-      }
+      if (u.cursor >= u.items.size()) continue;
+      const UnitState::Item item = u.items[u.cursor++];
+      rc = enqueue_subkernels<T>(g, ui, item.order_idx, u.ctiles[item.order_idx], item.ki0,
+                                 item.ki1);
       if (rc != PARALIA_OK) break;
-      if (u.cursor < total) work_left = true;
+      if (u.cursor < u.items.size()) work_left = true;
     }
     if (rc != PARALIA_OK) break;
   }
