@@ -210,8 +210,13 @@ def make_ctl(T: int = 0, units=None, cache_limit: int = 0, exec_streams: int = 0
     return ctl
 
 
-def init() -> None:
+DEFAULT_DB = PKG_DIR / "db_b200"   # measured on this pool's B200s by db_builder.py
+
+
+def init(load_default_db: bool = True) -> None:
     _check(lib().PARALiA_init())
+    if load_default_db and "PARALIA_DB" not in os.environ and (DEFAULT_DB / "Processed").is_dir():
+        load_database(str(DEFAULT_DB))
 
 
 def finalize() -> None:

@@ -88,13 +88,27 @@ int load_database(const char* dir) {
   if (L == 0) return fail(PARALIA_ERR_DB_MISSING, "model database not initialised");
   int found = 0;
   ModelDB db = g_db;
+  std::vector<std::vector<char>> have(L, std::vector<char>(L, 0));
   for (int d = 0; d < L; ++d)
     for (int s = 0; s < L; ++s) {
       if (d == s) continue;
       char name[512];
       snprintf(name, sizeof(name), "%s/Processed/Link-Stats_loc_dest-%d_loc_src-%d.log", dir, d - 1,
                s - 1);
-      if (read_link_file(name, &db.link[d][s])) ++found;
+      if (read_link_file(name, &db.link[d][s])) {
+        ++found;
+        have[d][s] = 1;
+      }
+    }
+  // The GPUs of the box are identical and sit behind one switch: a link that was not
+  // measured takes the model of the measured link of the same kind (host<->GPU 0 for
+  // every host link, GPU 1<-GPU 0 for every GPU pair).
+  for (int d = 0; d < L; ++d)
+    for (int s = 0; s < L; ++s) {
+      if (d == s || have[d][s]) continue;
+      if (s == 0 && d >= 1 && have[1][0]) db.link[d][s] = db.link[1][0];
+      else if (d == 0 && s >= 1 && have[0][1]) db.link[d][s] = db.link[0][1];
+      else if (d >= 1 && s >= 1 && L > 2 && have[2][1]) db.link[d][s] = db.link[2][1];
     }
   const char* funcs[2] = {"Dgemm", "Sgemm"};
   for (const char* f : funcs) {

@@ -3,8 +3,10 @@
 #include <chrono>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
+#include "autotune.hpp"
 #include "dgemm_tile.cuh"
 #include "sgemm_tile.cuh"
 
@@ -47,6 +49,11 @@ int Runtime::init() {
   devs_.assign(n, DeviceCtx());
   for (int d = 0; d < n; ++d) devs_[d].dev = d;
   inited_ = true;
+  // Calibration database named by the environment (reference: compile-time DEPLOYDB).
+  if (const char* db = getenv("PARALIA_DB")) {
+    reset_database_defaults(ndev_);
+    if (load_database(db) != PARALIA_OK) fprintf(stderr, "libparalia: %s\n", last_error_cstr());
+  }
   return PARALIA_OK;
 }
 

@@ -172,3 +172,14 @@ def test_runner_mask_parsing(pl):
     assert runner.parse_mask(8, "11111111") == list(range(8))
     with pytest.raises(SystemExit):
         runner.parse_mask(2, "0111")
+
+
+def test_packaged_database_loads_and_fills_unmeasured_links(pl):
+    # the database measured on one GPU serves every GPU of the box (identical links)
+    pl.load_database(str(pl.DEFAULT_DB))
+    t1 = pl.autotune_gemm(8, "N", "N", 32768, 32768, 32768, -1, -1, -1, pl.make_ctl(units=[0])).pred_t
+    t8 = pl.autotune_gemm(8, "N", "N", 32768, 32768, 32768, -1, -1, -1,
+                          pl.make_ctl(units=list(range(8)))).pred_t
+    # measured: 2.0 s on one GPU, 0.25 s of compute on eight
+    assert 1.8 < t1 < 2.3
+    assert 0.22 < t8 < 0.33
