@@ -159,6 +159,19 @@ int PARALiA_group_dgemm(char TransA, char TransB, int64_t Mloc, int64_t Nloc, in
                         double beta, double* C_block, int64_t ldC, int locC,
                         const paralia_ctl* ctl, paralia_report* out);
 
+int PARALiA_group_sgemm(char TransA, char TransB, int64_t Mloc, int64_t Nloc, int64_t K,
+                        float alpha, const float* A_panel, int64_t ldA, int locA,
+                        const float* B_panel, int64_t ldB, int locB,
+                        float beta, float* C_block, int64_t ldC, int locC,
+                        const paralia_ctl* ctl, paralia_report* out);
+
+/* Failure-detection self test (no counterpart in the reference, which has no failure
+ * detection): launches a kernel whose only wait can never be satisfied, with a clock
+ * budget of budget_ms. Returns PARALIA_ERR_TIMEOUT when the wait gave up, the kernel ended
+ * by itself and the error word reached the host -- the path every device-side wait of this
+ * library takes instead of hanging the GPU. The CUDA context stays usable afterwards. */
+int PARALiA_selftest_bounded_wait(int dev, double budget_ms);
+
 /* ---- per-tile kernels on device-resident data ---------------------------------------
  * What the reference reaches through backend_run_operation(params, "Dgemm"|"Sgemm"|
  * "Daxpy"|"Ddot", queue) (Library_scheduler/src/Subkernel.cpp:168,228; parameter blocks

@@ -125,6 +125,9 @@ SIGNATURES = {
     "PARALiA_group_finalize": (C.c_int, []),
     "PARALiA_group_dgemm": (C.c_int, [_chr, _chr, _i64, _i64, _i64, _dbl, _vp, _i64, C.c_int, _vp,
                                       _i64, C.c_int, _dbl, _vp, _i64, C.c_int, _ctl_p, _rep_p]),
+    "PARALiA_group_sgemm": (C.c_int, [_chr, _chr, _i64, _i64, _i64, _flt, _vp, _i64, C.c_int, _vp,
+                                      _i64, C.c_int, _flt, _vp, _i64, C.c_int, _ctl_p, _rep_p]),
+    "PARALiA_selftest_bounded_wait": (C.c_int, [C.c_int, _dbl]),
     "PARALiA_tile_dgemm": (C.c_int, [C.c_int, _vp, _chr, _chr, _i64, _i64, _i64, _dbl, _vp, _i64,
                                      _vp, _i64, _dbl, _vp, _i64]),
     "PARALiA_tile_sgemm": (C.c_int, [C.c_int, _vp, _chr, _chr, _i64, _i64, _i64, _flt, _vp, _i64,
@@ -260,6 +263,21 @@ def group_dgemm(TransA, TransB, Mloc, Nloc, K, alpha, A, ldA, B, ldB, beta, Cm, 
                                      locA, _ptr(B), ldB, locB, beta, _ptr(Cm), ldC, locC,
                                      C.byref(ctl) if ctl is not None else None, C.byref(rep)))
     return rep
+
+
+def group_sgemm(TransA, TransB, Mloc, Nloc, K, alpha, A, ldA, B, ldB, beta, Cm, ldC,
+                locA=LOC_AUTO, locB=LOC_AUTO, locC=LOC_AUTO, ctl: Ctl | None = None) -> Report:
+    rep = Report()
+    _check(lib().PARALiA_group_sgemm(_c(TransA), _c(TransB), Mloc, Nloc, K, alpha, _ptr(A), ldA,
+                                     locA, _ptr(B), ldB, locB, beta, _ptr(Cm), ldC, locC,
+                                     C.byref(ctl) if ctl is not None else None, C.byref(rep)))
+    return rep
+
+
+def selftest_bounded_wait(dev: int = 0, budget_ms: float = 1.0) -> None:
+    """Runs a kernel whose wait can never be satisfied; raises ParaliaError(ERR_TIMEOUT)
+    when the bounded wait gave up and reported to the host, as it must."""
+    _check(lib().PARALiA_selftest_bounded_wait(dev, budget_ms))
 
 
 def sgemm(TransA, TransB, M, N, K, alpha, A, ldA, B, ldB, beta, Cm, ldC,

@@ -342,6 +342,30 @@ int PARALiA_load_database(const char* dir) {
   return load_database(dir);
 }
 
+// Failure-detection self test: a kernel waits (bounded) for a signal that never comes.
+// Returns PARALIA_ERR_TIMEOUT when the give-up path worked, i.e. the kernel ended by
+// itself and reported through the device status word; the context stays usable.
+int PARALiA_selftest_bounded_wait(int dev, double budget_ms) {
+  if (!(budget_ms > 0.0) || budget_ms > 1000.0)
+    return fail(PARALIA_ERR_INVALID_ARG, "budget must be in (0, 1000] ms");
+  DeviceGuard guard;
+  PL_TRY(setup_device(dev));
+  int khz = 0;
+  PL_CUDA(cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, dev));
+  const long long clocks = (long long)(budget_ms * (double)khz);
+  PL_CUDA(launch_bounded_wait_selftest(Runtime::get().dev(dev).status_dev, clocks, nullptr));
+  PL_CUDA(cudaDeviceSynchronize());
+  return Runtime::get().check_status(dev);
+}
+
+int PARALiA_group_sgemm(char TransA, char TransB, int64_t Mloc, int64_t Nloc, int64_t K,
+                        float alpha, const float* A, int64_t ldA, int locA, const float* B,
+                        int64_t ldB, int locB, float beta, float* C, int64_t ldC, int locC,
+                        const paralia_ctl* ctl, paralia_report* out) {
+  return exec_group_sgemm(TransA, TransB, Mloc, Nloc, K, alpha, A, ldA, locA, B, ldB, locB, beta,
+                          C, ldC, locC, ctl, out);
+}
+
 // ------------------------------ calibration ------------------------------
 
 int PARALiA_bench_dmma_peak(int dev, int shape, int iters, double* tflops) {

@@ -353,7 +353,29 @@ __global__ void __launch_bounds__(256) dmma_peak_kernel(int iters, double* sink)
   if (s == 123.456) sink[0] = s;  // keeps the loop alive without real traffic
 }
 
+// Waits on a barrier that nothing will ever complete, with a short clock budget: the wait
+// must give up, record its error word and let the kernel end normally.
+__global__ void bounded_wait_selftest_kernel(int* status, long long budget_clocks) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (!mbar_wait_bounded(&bar, 0, &abort_flag, budget_clocks))
+      atomicExch(status, KERR_FULL_WAIT_TIMEOUT);
+  }
+}
+
 }  // namespace
+
+cudaError_t launch_bounded_wait_selftest(int* status, long long budget_clocks, cudaStream_t stream) {
+  bounded_wait_selftest_kernel<<<1, 32, 0, stream>>>(status, budget_clocks);
+  return cudaGetLastError();
+}
 
 cudaError_t dgemm_tile_configure() {
   cudaError_t e;

@@ -54,6 +54,10 @@ cudaError_t launch_dgemm_generic(char ta, char tb, int M, int N, int K, double a
 // Opt the kernels into their dynamic shared memory size; once per device.
 cudaError_t dgemm_tile_configure();
 
+// One warp waits on an mbarrier that never completes, for at most budget_clocks, then
+// writes a KERR_* code to *status: exercises the give-up path of every bounded wait.
+cudaError_t launch_bounded_wait_selftest(int* status, long long budget_clocks, cudaStream_t stream);
+
 // Register-only DMMA throughput loop. shape in {884, 1684, 1688, 16816}.
 cudaError_t launch_dmma_peak(int shape, int iters, int blocks, double* sink, cudaStream_t stream);
 

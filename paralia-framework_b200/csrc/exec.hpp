@@ -17,6 +17,10 @@ int exec_group_dgemm(char ta, char tb, int64_t M, int64_t N, int64_t K, double a
                      int locB, double beta, double* C, int64_t ldC, int locC,
                      const paralia_ctl* ctl, paralia_report* out);
 
+int exec_group_sgemm(char ta, char tb, int64_t M, int64_t N, int64_t K, float alpha, const float* A,
+                     int64_t ldA, int locA, const float* B, int64_t ldB, int locB, float beta,
+                     float* C, int64_t ldC, int locC, const paralia_ctl* ctl, paralia_report* out);
+
 int exec_sgemm(char ta, char tb, int64_t M, int64_t N, int64_t K, float alpha, const float* A,
                int64_t ldA, int locA, const float* B, int64_t ldB, int locB, float beta, float* C,
                int64_t ldC, int locC, const paralia_ctl* ctl, paralia_report* out);

@@ -991,4 +991,13 @@ int exec_group_dgemm(char ta, char tb, int64_t M, int64_t N, int64_t K, double a
                           ctl, out, "Dgemm", grp);
 }
 
+int exec_group_sgemm(char ta, char tb, int64_t M, int64_t N, int64_t K, float alpha, const float* A,
+                     int64_t ldA, int locA, const float* B, int64_t ldB, int locB, float beta,
+                     float* C, int64_t ldC, int locC, const paralia_ctl* ctl, paralia_report* out) {
+  Group* grp = Group::current();
+  if (!grp) return fail(PARALIA_ERR_INVALID_ARG, "PARALiA_group_init has not been called");
+  return run_gemm<float>(ta, tb, M, N, K, alpha, A, ldA, locA, B, ldB, locB, beta, C, ldC, locC,
+                         ctl, out, "Sgemm", grp);
+}
+
 }  // namespace paralia

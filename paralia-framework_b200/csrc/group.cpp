@@ -8,6 +8,7 @@
 #include <atomic>
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 
@@ -18,7 +19,16 @@ namespace paralia {
 
 namespace {
 constexpr uint32_t SHM_MAGIC = 0x50414c47u;  // "PALG"
-constexpr double BARRIER_TIMEOUT_MS = 60000.0;
+// How long a rank waits for the others at a hand-shake before it reports a missing rank.
+static double barrier_timeout_ms() {
+  static const double v = [] {
+    const char* e = getenv("PARALIA_GROUP_TIMEOUT_MS");
+    const double t = e ? atof(e) : 0.0;
+    return t > 0.0 ? t : 60000.0;
+  }();
+  return v;
+}
+#define BARRIER_TIMEOUT_MS (barrier_timeout_ms())
 Group* g_group = nullptr;
 }  // namespace
 
@@ -118,8 +128,17 @@ int Group::init(const char* name, int rank, int world, int dev) {
   g->shm_->attached.fetch_add(1);
   g_group = g;
   int rc = g->barrier();
-  if (rc != PARALIA_OK) return rc;
-  if (rank == 0) shm_unlink(g->shm_name_);  // every rank has it mapped; the name can go
+  if (rank == 0) shm_unlink(g->shm_name_);  // every rank has it mapped (or never will)
+  if (rc != PARALIA_OK) {
+    // a rank never arrived: leave no half-built group behind
+    for (int i = 0; i < GROUP_MAX_EVENTS; ++i)
+      if (g->own_ev_[i]) cudaEventDestroy(g->own_ev_[i]);
+    munmap(g->shm_, g->shm_bytes_);
+    cudaGetLastError();
+    delete g;
+    g_group = nullptr;
+    return rc;
+  }
   return PARALIA_OK;
 }
 

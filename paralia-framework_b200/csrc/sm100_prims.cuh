@@ -56,7 +56,8 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
 // Wait for `parity` of `bar`. Returns false if the budget ran out or another thread of
 // the CTA already raised *abort_flag (a shared-memory word).
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,
-                                                  volatile int* abort_flag) {
+                                                  volatile int* abort_flag,
+                                                  long long budget = WAIT_BUDGET_CLOCKS) {
   if (mbar_test(bar, parity)) return true;
   long long t0 = clock64();
   uint32_t polls = 0;
@@ -64,7 +65,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     if (mbar_test(bar, parity)) return true;
     if ((++polls & 255u) == 0) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > WAIT_BUDGET_CLOCKS) return false;
+      if (clock64() - t0 > budget) return false;
     }
   }
 }

@@ -100,3 +100,45 @@ def test_group_four_ranks_share_a_and_b(orc, tmp_path):
     szA, szB, szC = M * K * 8, K * N * 8, M * N * 8
     assert h2d == szA + szB + szC
     assert p2p == szA + szB
+
+
+def _sgemm_worker(rank, world, name, M, N, K, T, out_dir):
+    sys.path.insert(0, str(ROOT))
+    import importlib
+    import __graft_entry__ as entry
+    pl = entry.load_package()
+    ranks = importlib.import_module("paralia_framework_b200.ranks")
+    orc = entry.load_oracle()
+    pl.group_init(name, rank, world, rank)
+    (m0, m1), (n0, n1), _, _ = ranks.gemm_block(rank, world, M, N, quantum=T)
+    A = orc.uniform_f32(M * K, 42).reshape((M, K), order="F")
+    B = orc.uniform_f32(K * N, 43).reshape((K, N), order="F")
+    C = orc.uniform_f32(M * N, 44).reshape((M, N), order="F")
+    Ap, Bp = np.asfortranarray(A[m0:m1, :]), np.asfortranarray(B[:, n0:n1])
+    Cb = np.asfortranarray(C[m0:m1, n0:n1])
+    rep = pl.group_sgemm("N", "N", m1 - m0, n1 - n0, K, 1.25, Ap, m1 - m0, Bp, K, 0.75, Cb, m1 - m0,
+                         ctl=pl.make_ctl(T=T))
+    np.save(os.path.join(out_dir, f"S_{rank}.npy"), Cb)
+    np.save(os.path.join(out_dir, f"sb_{rank}.npy"), np.array([rep.h2d_bytes, rep.p2p_bytes, m0, m1, n0, n1]))
+    pl.group_finalize()
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs two GPUs")
+def test_group_sgemm_two_ranks(orc, tmp_path):
+    import torch.multiprocessing as mp
+    M, N, K, T = 1024, 768, 512, 256
+    mp.spawn(_sgemm_worker, args=(2, f"s{os.getpid()}", M, N, K, T, str(tmp_path)), nprocs=2, join=True)
+    A = orc.uniform_f32(M * K, 42).reshape((M, K), order="F")
+    B = orc.uniform_f32(K * N, 43).reshape((K, N), order="F")
+    C = orc.uniform_f32(M * N, 44).reshape((M, N), order="F")
+    want = 1.25 * (A.astype(np.float64) @ B.astype(np.float64)) + 0.75 * C.astype(np.float64)
+    got = np.zeros((M, N))
+    h2d = p2p = 0
+    for r in range(2):
+        b = np.load(tmp_path / f"sb_{r}.npy")
+        m0, m1, n0, n1 = (int(v) for v in b[2:6])
+        got[m0:m1, n0:n1] = np.load(tmp_path / f"S_{r}.npy")
+        h2d += int(b[0]); p2p += int(b[1])
+    assert orc.normwise_rel_err(got, want) <= 4 * K * 2.0 ** -23
+    assert h2d == (M * K + K * N + M * N) * 4     # every host tile crosses the host link once
+    assert p2p > 0                                # B tiles reach the other rank packed, over NVLink
