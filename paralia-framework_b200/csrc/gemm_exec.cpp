@@ -59,6 +59,18 @@ struct UnitState {
   std::vector<Resident> a, b, c, csrc; // indexed by tile id of each operand
   int next_block = 0;
   int nblocks = 0;
+  // Bounded cache (only when the slab cannot hold every tile the unit touches): what each
+  // block holds, who may still be reading it, and blocks handed back after a write-back.
+  struct BlockInfo {
+    int kind = 0;            // 0 free, 1 A tile, 2 B tile, 3 C accumulator / original C
+    int64_t tid = -1;
+    uint64_t last_seq = 0;   // launch number that last used it
+    cudaEvent_t readers[MAX_EXEC_STREAMS] = {};
+    cudaEvent_t freed = nullptr;
+  };
+  std::vector<BlockInfo> blocks;
+  std::vector<int> free_blocks;
+  uint64_t seq = 0;          // launches enqueued so far
   CUtensorMap map_slab_kc, map_slab_mn;   // tile cache seen k-contiguous / row-contiguous
   CUtensorMap map_a_native, map_b_native; // user matrices on this GPU
   bool a_native_ok = false, b_native_ok = false, c_native = false;
@@ -85,9 +97,11 @@ struct GemmCall {
   bool share_a = false, share_b = false;   // tiles shared inside the grid row / column
   int nA = 0, nB = 0;                       // fixed block ranges of A and B tiles in group mode
   bool prefetch_phase = false;              // enqueueing only this rank's home tiles
+  bool evict = false;                       // the slab is smaller than the working set
+  int64_t evictions = 0;
   // Write-backs held until the unit's host->GPU stream has drained (see run_gemm).
   bool defer_wb = false;
-  struct PendingWb { int ui; cudaEvent_t done; char* dst; int64_t dst_ld; const char* src; int64_t rows, cols; };
+  struct PendingWb { int ui; int ct; cudaEvent_t done; char* dst; int64_t dst_ld; const char* src; int64_t rows, cols; };
   std::vector<PendingWb> pending_wb;
   std::vector<UnitState> units;
   std::vector<int> ctile_owner;             // C tile -> unit index
@@ -189,12 +203,61 @@ TileGeom<T> geom_b(const GemmCall<T>& g, int64_t ki, int64_t ni) {
   return t;
 }
 
+// Hand out a cache block for tile `tid` of `kind` (1 A, 2 B, 3 C). While fresh blocks
+// remain they are used in order. In bounded-cache mode a block returned after a write-back
+// is reused next, else the least recently used A/B tile that the current launch does not
+// need is evicted (the reference recycles blocks of a clamped slab the same way,
+// dgemm.cpp:80-94; its policy lives in the backend that is not part of the checkout).
+// Every stream that may fill the block waits for the kernels and copies still using it.
 template <typename T>
-int take_block(GemmCall<T>& g, UnitState& u, int* blk) {
-  if (u.next_block >= u.nblocks)
+int take_block(GemmCall<T>& g, UnitState& u, int* blk, int kind = 0, int64_t tid = -1,
+               cudaStream_t extra_writer = nullptr) {
+  if (u.next_block < u.nblocks) {
+    *blk = u.next_block++;
+    if (g.evict) {
+      UnitState::BlockInfo& bi = u.blocks[*blk];
+      bi.kind = kind; bi.tid = tid; bi.last_seq = u.seq;
+    }
+    return PARALIA_OK;
+  }
+  if (!g.evict)
     return fail(PARALIA_ERR_OUT_OF_MEMORY, "GPU %d: tile cache of %d blocks exhausted", u.dev,
                 u.nblocks);
-  *blk = u.next_block++;
+  int pick = -1;
+  if (!u.free_blocks.empty()) {
+    pick = u.free_blocks.back();
+    u.free_blocks.pop_back();
+  } else {
+    uint64_t oldest = UINT64_MAX;
+    for (int b = 0; b < u.nblocks; ++b) {
+      const UnitState::BlockInfo& bi = u.blocks[b];
+      if ((bi.kind == 1 || bi.kind == 2) && bi.last_seq < u.seq && bi.last_seq < oldest) {
+        oldest = bi.last_seq;
+        pick = b;
+      }
+    }
+    if (pick < 0)
+      return fail(PARALIA_ERR_OUT_OF_MEMORY,
+                  "GPU %d: a tile cache of %d blocks is too small for one launch", u.dev, u.nblocks);
+    UnitState::BlockInfo& v = u.blocks[pick];
+    Resident& r = v.kind == 1 ? u.a[v.tid] : u.b[v.tid];
+    r.present = false;
+    r.block = -1;
+    g.evictions += 1;
+  }
+  UnitState::BlockInfo& bi = u.blocks[pick];
+  DeviceCtx& dc = Runtime::get().dev(u.dev);
+  PL_CUDA(cudaSetDevice(u.dev));
+  cudaStream_t writers[4] = {dc.h2d, dc.p2p, dc.pack, extra_writer};
+  for (cudaStream_t w : writers) {
+    if (!w) continue;
+    for (int i = 0; i < MAX_EXEC_STREAMS; ++i)
+      if (bi.readers[i]) PL_CUDA(cudaStreamWaitEvent(w, bi.readers[i], 0));
+    if (bi.freed) PL_CUDA(cudaStreamWaitEvent(w, bi.freed, 0));
+  }
+  bi = UnitState::BlockInfo();
+  bi.kind = kind; bi.tid = tid; bi.last_seq = u.seq;
+  *blk = pick;
   return PARALIA_OK;
 }
 
@@ -307,7 +370,7 @@ int ensure_input_f32(GemmCall<T>& g, int ui, bool is_a, int64_t i0, int64_t i1) 
     return PARALIA_OK;
   }
   if (g.grp) r.block = is_a ? (int)tid : g.nA + (int)tid;
-  else PL_TRY(take_block(g, u, &r.block));
+  else PL_TRY(take_block(g, u, &r.block, is_a ? 1 : 2, tid));
   PL_TRY(rt.get_event(u.dev, &r.ready));
   int home = ui;
   if (op.loc == -1 && !g.grp) {
@@ -390,7 +453,7 @@ int ensure_input(GemmCall<T>& g, int ui, bool is_a, int64_t i0, int64_t i1) {
     return PARALIA_OK;
   }
   if (g.grp) r.block = is_a ? (int)tid : g.nA + (int)tid;   // fixed slots in group mode
-  else PL_TRY(take_block(g, u, &r.block));
+  else PL_TRY(take_block(g, u, &r.block, is_a ? 1 : 2, tid));
   PL_TRY(rt.get_event(u.dev, &r.ready));
   if (op.loc == -1) {
     // Host-resident tile: one consumer (its "home") pulls it over its host link, the
@@ -440,7 +503,7 @@ int ensure_csrc(GemmCall<T>& g, int ui, int ct) {
   DeviceCtx& dc = rt.dev(u.dev);
   const int64_t mi = ct / g.Nt, ni = ct % g.Nt;
   PL_CUDA(cudaSetDevice(u.dev));
-  PL_TRY(take_block(g, u, &rs.block));
+  PL_TRY(take_block(g, u, &rs.block, 3, ct));
   PL_TRY(rt.get_event(u.dev, &rs.ready));
   const char* src = (const char*)g.C.ptr + (mi * g.Tt + ni * g.Tt * g.C.ld) * g.esz;
   const int64_t nr = g.mrows(mi), nc = g.ncols(ni);
@@ -466,6 +529,20 @@ int issue_writeback(GemmCall<T>& g, const typename GemmCall<T>::PendingWb& wb) {
                             (size_t)wb.rows * g.esz, wb.cols, cudaMemcpyDefault, dc.d2h));
   if (g.C.loc == -1) g.rep->d2h_bytes += wb.rows * wb.cols * g.esz;
   else g.rep->p2p_bytes += wb.rows * wb.cols * g.esz;
+  if (g.evict) {
+    // the accumulator and original-C blocks of this tile can be reused once it is home
+    cudaEvent_t home;
+    PL_TRY(Runtime::get().get_event(u.dev, &home));
+    PL_CUDA(cudaEventRecord(home, dc.d2h));
+    const int ct = wb.ct;
+    for (Resident* r : {&u.c[ct], &u.csrc[ct]})
+      if (r->block >= 0) {
+        u.blocks[r->block] = UnitState::BlockInfo();
+        u.blocks[r->block].freed = home;
+        u.free_blocks.push_back(r->block);
+        r->block = -1;
+      }
+  }
   return PARALIA_OK;
 }
 
@@ -484,12 +561,20 @@ int enqueue_subkernels(GemmCall<T>& g, int ui, int order_idx, int ct, int ki0, i
   const int sidx = order_idx % g.exec_streams;
   cudaStream_t es = dc.exec[sidx];
   PL_CUDA(cudaSetDevice(u.dev));
+  ++u.seq;   // tiles taken from here on belong to this launch and cannot be evicted by it
 
   typename TileKernel<T>::Args args;
   memset(&args, 0, sizeof(args));
   args.nparts = 0;
   bool a_native = false, b_native = false;
   for (int ki = ki0; ki < ki1; ++ki) {
+    if (g.evict) {
+      // a tile that is already cached must survive the fetch of its partner
+      Resident& pa = u.a[mi * g.Kt + ki];
+      Resident& pb = u.b[ki * g.Nt + ni];
+      if (pa.present && pa.block >= 0) u.blocks[pa.block].last_seq = u.seq;
+      if (pb.present && pb.block >= 0) u.blocks[pb.block].last_seq = u.seq;
+    }
     PL_TRY(ensure_input(g, ui, true, mi, ki));
     PL_TRY(ensure_input(g, ui, false, ki, ni));
     PL_CUDA(cudaSetDevice(u.dev));
@@ -517,7 +602,7 @@ int enqueue_subkernels(GemmCall<T>& g, int ui, int order_idx, int ct, int ki0, i
   if (!rc.present) {
     rc.present = true;
     if (u.c_native) rc.native = true;
-    else PL_TRY(take_block(g, u, &rc.block));
+    else PL_TRY(take_block(g, u, &rc.block, 3, ct, es));
   }
   args.M = (int32_t)g.mrows(mi);
   args.N = (int32_t)g.ncols(ni);
@@ -563,10 +648,20 @@ int enqueue_subkernels(GemmCall<T>& g, int ui, int order_idx, int ct, int ki0, i
   PL_TRY(rt.get_event(u.dev, &done));
   PL_CUDA(cudaEventRecord(done, es));
   u.exec_tail[sidx] = done;
+  if (g.evict) {
+    for (int ki = ki0; ki < ki1; ++ki) {
+      const Resident* rr[2] = {&u.a[mi * g.Kt + ki], &u.b[ki * g.Nt + ni]};
+      for (const Resident* r : rr)
+        if (!r->native && r->block >= 0) {
+          u.blocks[r->block].readers[sidx] = done;
+          u.blocks[r->block].last_seq = u.seq;
+        }
+    }
+  }
   if (last && !rc.native) {
     // Write the finished tile back to where C lives (reference: WBTileMap, dgemm.cpp:583).
     char* dst = (char*)g.C.ptr + (mi * g.Tt + ni * g.Tt * g.C.ld) * g.esz;
-    typename GemmCall<T>::PendingWb wb{ui, done, dst, g.C.ld, g.block_ptr(u, rc.block),
+    typename GemmCall<T>::PendingWb wb{ui, ct, done, dst, g.C.ld, g.block_ptr(u, rc.block),
                                       (int64_t)args.M, (int64_t)args.N};
     if (g.defer_wb && g.C.loc == -1) g.pending_wb.push_back(wb);
     else PL_TRY(issue_writeback(g, wb));
@@ -589,8 +684,8 @@ int kchain_len(const GemmCall<T>& g, int ki0) {
     const char* e = getenv("PARALIA_KCHAIN");   // experiments only: changes rounding
     return e ? atoi(e) : 0;
   }();
-  (void)g;
-  int len = forced > 0 ? forced : (ki0 == 0 ? 1 : 4);
+  // a bounded cache keeps only one A and one B tile per launch alive
+  int len = g.evict ? 1 : (forced > 0 ? forced : (ki0 == 0 ? 1 : 4));
   len = std::min<int>(len, DG_MAX_PARTS);
   return std::max(len, 1);
 }
@@ -620,6 +715,7 @@ void build_items(const GemmCall<T>& g, UnitState& u) {
   const int kt = (int)std::max<int64_t>(g.Kt, 1);
   // about four bands per unit, between 4 and 16 C tiles each (measured best at 4 GPUs)
   int band = band_env > 0 ? band_env : std::min(16, std::max(4, (n + 3) / 4));
+  if (g.evict) band = 1;   // tile-major: one accumulator alive at a time
   u.items.clear();
   for (int b0 = 0; b0 < n; b0 += band) {
     const int b1 = std::min(n, b0 + band);
@@ -796,12 +892,41 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
       if (g.B.loc == -1) need += 0;
     }
     if (!u.c_native) need += (int64_t)u.ctiles.size() * ((beta != (T)0) ? 2 : 1);
-    u.nblocks = (int)need;
-    size_t bytes = (size_t)need * g.block_bytes();
-    if (eff_ctl.cache_limit > 0 && bytes > (size_t)eff_ctl.cache_limit)
-      return fail_out(fail(PARALIA_ERR_OUT_OF_MEMORY,
-                           "GPU %d needs %zu bytes of tile cache but cache_limit is %lld", u.dev,
-                           bytes, (long long)eff_ctl.cache_limit));
+    // The slab is clamped by the caller's cache_limit and by what the GPU has left
+    // (reference: min(cache_limit, free - 30 % of total), dgemm.cpp:53-54,80-87; here 90 %
+    // of free memory plus the slab already held). A clamped slab recycles its blocks.
+    int64_t cap = need;
+    if (eff_ctl.cache_limit > 0) cap = std::min<int64_t>(cap, eff_ctl.cache_limit / (int64_t)g.block_bytes());
+    {
+      size_t free_b = 0, total_b = 0;
+      if (cudaSetDevice(u.dev) == cudaSuccess && cudaMemGetInfo(&free_b, &total_b) == cudaSuccess) {
+        const double avail = 0.9 * ((double)free_b + (double)rt.dev(u.dev).slab_bytes);
+        cap = std::min<int64_t>(cap, (int64_t)(avail / (double)g.block_bytes()));
+      } else {
+        cudaGetLastError();
+      }
+    }
+    if (cap < need) {
+      const int64_t min_blocks = (u.c_native ? 0 : (beta != (T)0 ? 2 : 1)) +
+                                 (u.a_native_ok ? 0 : 1) + (u.b_native_ok ? 0 : 1);
+      if (grp)
+        return fail_out(fail(PARALIA_ERR_OUT_OF_MEMORY,
+                             "GPU %d: the tile cache (%lld of %lld blocks) is too small; process "
+                             "groups need the whole working set cached",
+                             u.dev, (long long)cap, (long long)need));
+      if (cap < min_blocks)
+        return fail_out(fail(PARALIA_ERR_OUT_OF_MEMORY,
+                             "GPU %d needs at least %lld cache blocks of %zu bytes but only %lld fit "
+                             "(cache_limit %lld)",
+                             u.dev, (long long)min_blocks, g.block_bytes(), (long long)cap,
+                             (long long)eff_ctl.cache_limit));
+      g.evict = true;
+      g.peer_fetch = false;   // every GPU fetches for itself: a block may be recycled at any time
+    }
+    u.nblocks = (int)cap;
+    u.blocks.assign((size_t)cap, UnitState::BlockInfo());
+    u.free_blocks.clear();
+    size_t bytes = (size_t)cap * g.block_bytes();
     if (grp) {
       // collective: agree on sharing, exchange slab handles (group.hpp)
       g.nA = u.a_native_ok ? 0 : (int)(g.Mt * g.Kt);
@@ -870,6 +995,7 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
   {
     const char* e = getenv("PARALIA_DEFER_WB");
     g.defer_wb = e ? atoi(e) != 0 : (grp ? grp->world() : active) >= 4;
+    if (g.evict) g.defer_wb = false;   // blocks are needed back as soon as a tile is home
   }
   if (grp) {
     // Group mode, phase 1: enqueue the host fetches of the tiles this rank is the home of

@@ -235,9 +235,46 @@ def test_dgemm_cache_limit_too_small(pl, orc):
     M = N = K = 512
     A, B, C, lda, ldb, ldc = _case(orc, "N", "N", M, N, K)
     with pytest.raises(pl.ParaliaError) as e:
-        pl.dgemm("N", "N", M, N, K, 1.0, A, lda, B, ldb, 0.0, C, ldc,
+        pl.dgemm("N", "N", M, N, K, 1.0, A, lda, B, ldb, 0.5, C, ldc,
                  ctl=pl.make_ctl(T=128, units=[0], cache_limit=3 * 128 * 128 * 8))
-    assert e.value.code == pl.ERR_OUT_OF_MEMORY
+    assert e.value.code == pl.ERR_OUT_OF_MEMORY       # beta != 0 needs A, B, accumulator, original C
+
+
+@pytest.mark.parametrize("ta,tb", [("N", "N"), ("T", "N"), ("N", "T")])
+@pytest.mark.parametrize("blocks", [4, 7, 20])
+def test_dgemm_bounded_cache_recycles_blocks(pl, orc, ta, tb, blocks):
+    # the reference's "run_large" cases (dgemm_tester.cpp:284-403): a cache far smaller than
+    # the working set (64 blocks here) still gives the right answer, at the price of
+    # fetching tiles more than once
+    M, N, K, T = 1024, 1024, 1024, 256
+    A, B, C, lda, ldb, ldc = _case(orc, ta, tb, M, N, K)
+    want = C.copy(order="F")
+    orc.dgemm_tiled(ta, tb, M, N, K, 1.23, A, lda, B, ldb, 0.9876, want, ldc, T)
+    rep = pl.dgemm(ta, tb, M, N, K, 1.23, A, lda, B, ldb, 0.9876, C, ldc,
+                   ctl=pl.make_ctl(T=T, units=[0], cache_limit=blocks * T * T * 8))
+    assert orc.normwise_rel_err(C, want) <= tol(K)
+    minimal = (M * K + K * N + M * N) * 8
+    assert rep.h2d_bytes > minimal
+    assert rep.d2h_bytes == M * N * 8
+    # a larger cache re-fetches less
+    if blocks == 4:
+        rep2 = pl.dgemm(ta, tb, M, N, K, 1.23, A, lda, B, ldb, 0.0, C, ldc,
+                        ctl=pl.make_ctl(T=T, units=[0], cache_limit=24 * T * T * 8))
+        rep3 = pl.dgemm(ta, tb, M, N, K, 1.23, A, lda, B, ldb, 0.0, C, ldc,
+                        ctl=pl.make_ctl(T=T, units=[0], cache_limit=4 * T * T * 8))
+        assert rep2.h2d_bytes < rep3.h2d_bytes
+
+
+def test_dgemm_bounded_cache_is_deterministic(pl, orc):
+    M, N, K, T = 768, 768, 1024, 256
+    A, B, C0, lda, ldb, ldc = _case(orc, "N", "N", M, N, K)
+    outs = []
+    for _ in range(2):
+        C = C0.copy(order="F")
+        pl.dgemm("N", "N", M, N, K, 1.23, A, lda, B, ldb, 0.9876, C, ldc,
+                 ctl=pl.make_ctl(T=T, units=[0], cache_limit=6 * T * T * 8))
+        outs.append(C)
+    assert np.array_equal(outs[0], outs[1])
 
 
 def test_fill_same_bits_on_host_and_device(pl, orc):

@@ -121,6 +121,20 @@ def test_level1_two_gpus(pl, orc):
 
 
 @need2
+def test_dgemm_two_gpus_bounded_cache(pl, orc):
+    M, N, K, T = 1024, 1024, 768, 256
+    A = orc.matrix_f64(M, K, 42)
+    B = orc.matrix_f64(K, N, 43)
+    C = orc.matrix_f64(M, N, 44)
+    want = C.copy(order="F")
+    orc.dgemm_tiled("N", "N", M, N, K, 1.23, A, M, B, K, 0.9876, want, M, T)
+    rep = pl.dgemm("N", "N", M, N, K, 1.23, A, M, B, K, 0.9876, C, M,
+                   ctl=pl.make_ctl(T=T, units=[0, 1], cache_limit=8 * T * T * 8))
+    assert orc.normwise_rel_err(C, want) <= 8 * K * EPS64
+    assert rep.p2p_bytes == 0 and rep.h2d_bytes > (M * K + K * N + M * N) * 8
+
+
+@need2
 def test_sgemm_two_gpus(pl, orc):
     M, N, K, T = 1024, 768, 512, 256
     A = orc.uniform_f32(M * K, 42).reshape((M, K), order="F")

@@ -133,3 +133,14 @@ def test_sgemm_k_zero(pl, orc):
     B = np.zeros((1, N), dtype=np.float32, order="F")
     pl.sgemm("N", "N", M, N, 0, 1.0, A, M, B, 1, 0.5, C, M, ctl=pl.make_ctl(units=[0]))
     np.testing.assert_allclose(C, want, rtol=1e-6)
+
+
+def test_sgemm_bounded_cache(pl, orc):
+    M, N, K, T = 1024, 768, 1024, 256
+    A, B, C, ar, br = _inputs(orc, "N", "T", M, N, K)
+    want = _want("N", "T", M, N, K, 1.25, 0.75, A, B, C, ar, br)
+    blk = 2 * 256 * 256 * 4          # packed FP32 tile (hi + lo planes)
+    rep = pl.sgemm("N", "T", M, N, K, 1.25, A, ar, B, br, 0.75, C, M,
+                   ctl=pl.make_ctl(T=T, units=[0], cache_limit=6 * blk))
+    assert orc.normwise_rel_err(C, want) <= tol(K)
+    assert rep.h2d_bytes > (M * K + K * N + M * N) * 4
