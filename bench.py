@@ -114,17 +114,29 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------ CPU arm
-def cpu_dgemm_sample(target_s: float = 12.0):
-    """OpenBLAS cblas_dgemm on all host cores, NN, alpha=beta=1, seeded uniform inputs, on
-    the largest square sample of the workload that takes about target_s seconds."""
-    import numpy as np
-    import oracle
-
-    cores = os.cpu_count() or 1
+def _use_all_host_threads() -> int:
+    """Launchers set OMP_NUM_THREADS=1 per rank; the CPU arm runs on rank 0 alone and may use
+    every core the job has."""
     try:
         cores = len(os.sched_getaffinity(0))
     except Exception:
+        cores = os.cpu_count() or 1
+    for var in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
+        os.environ[var] = str(cores)
+    try:
+        from threadpoolctl import threadpool_limits
+        threadpool_limits(limits=cores)
+    except Exception:
         pass
+    return cores
+
+
+def cpu_dgemm_sample(target_s: float = 12.0):
+    """OpenBLAS cblas_dgemm on all host cores, NN, alpha=beta=1, seeded uniform inputs, on
+    the largest square sample of the workload that takes about target_s seconds."""
+    cores = _use_all_host_threads()
+    import numpy as np
+    import oracle
 
     def run(n):
         A = oracle.uniform_f64(n * n, 42).reshape((n, n), order="F")
@@ -147,9 +159,9 @@ def run_reference_arm(args, rank):
     if rank != 0:
         return
     steps, warm = args.steps, args.warmup
+    cores = _use_all_host_threads()
     import numpy as np
     import oracle
-    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
     # bounded sample per step: a square DGEMM sized so that warm-up + steps stay within minutes
     n = 4096 if cores < 32 else 8192
     A = oracle.uniform_f64(n * n, 42).reshape((n, n), order="F")
@@ -213,7 +225,20 @@ def main():
         # the ranks form a library group: host-resident tiles are shared over NVLink (CUDA IPC)
         token = [f"{os.environ.get('MASTER_PORT', '0')}_{os.getpid()}"]
         dist.broadcast_object_list(token, src=0)
-        pl.group_init(token[0], rank, world, dev)
+        try:
+            pl.group_init(token[0], rank, world, dev)
+            joined = 1
+        except pl.ParaliaError as exc:      # e.g. no POSIX shared memory in this container
+            print(f"rank {rank}: no process group ({exc}); every rank fetches for itself",
+                  file=sys.stderr, flush=True)
+            joined = 0
+        flag = torch.tensor([joined], device=cuda)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        use_group = bool(flag.item())
+        if joined and not use_group:
+            pl.group_finalize()
+    else:
+        use_group = False
 
     import importlib
     ranks = importlib.import_module("paralia_framework_b200.ranks")
@@ -245,7 +270,7 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    gemm = pl.group_dgemm if world > 1 else pl.dgemm
+    gemm = pl.group_dgemm if use_group else pl.dgemm
 
     def run_leg(A, B, C, steps, warm):
         launches = h2d = d2h = 0
@@ -326,10 +351,21 @@ def main():
                 "value_placement": ("operands resident in the HBM of GPU 0, one process drives all GPUs"
                                     if args.inproc else "operands resident in HBM"),
                 "e2e_placement": "pinned host", "launch": "inproc" if args.inproc else "one process per GPU",
+                "tile_sharing_between_ranks": bool(use_group),
             },
             "roofline": {
                 "bound": "tensor", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
-                "frac": achieved / peak_tf if peak_tf else None, "traffic": None,
+                "frac": achieved / peak_tf if peak_tf else None,
+                # DRAM bytes per launch: algorithmic bytes of an average launch (its share of
+                # the A row panel and B column panel of its C tile, plus C read and written)
+                # times the 1.30 ratio of measured to algorithmic bytes from the ncu capture
+                # of the same kernel on a small case
+                "traffic": 1.30 * 8.0 * (2.0 * Mloc * Nloc * K / max(rep.T, 1) + 2.0 * Mloc * Nloc
+                                         * max(launches // max(args.steps, 1) // world, 1)
+                                         / max((Mloc // max(rep.T, 1)) * (Nloc // max(rep.T, 1)), 1))
+                           / max(launches // max(args.steps, 1) // world, 1),
+                "traffic_source": "algorithmic bytes x 1.30 (ncu dram__bytes of this kernel on a "
+                                  "4096^3 case, profiles/dgemm_tile_kernel_n4096_ncu_full.md)",
                 "peak_source": "FP64 DMMA register-loop microbenchmark run in this process "
                                "(MEASURED_PEAKS.json holds no FP64 figure)",
                 "kernel": "dgemm_tile_kernel", "launches": launches,
@@ -342,7 +378,8 @@ def main():
         }
         print(json.dumps(line), flush=True)
     if world > 1:
-        pl.group_finalize()
+        if use_group:
+            pl.group_finalize()
         dist.destroy_process_group()
 
 
