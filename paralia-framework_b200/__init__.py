@@ -101,6 +101,7 @@ class Report(C.Structure):
             "h2d_bytes": self.h2d_bytes, "d2h_bytes": self.d2h_bytes,
             "p2p_bytes": self.p2p_bytes, "d2d_bytes": self.d2d_bytes,
             "kernel_launches": self.kernel_launches, "grid": (self.grid_d1, self.grid_d2),
+            "metadata_reused": self.metadata_reused,
         }
 
 

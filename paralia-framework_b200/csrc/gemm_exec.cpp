@@ -16,7 +16,10 @@
 // fetches it still needs and its kernel; dependencies are CUDA events only.
 #include <algorithm>
 #include <cstdlib>
+#include <cstdio>
 #include <cstring>
+#include <map>
+#include <string>
 #include <type_traits>
 #include <vector>
 
@@ -806,9 +809,30 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
     eff_ctl.active_unit_id_list[0] = grp->dev();
     g.grp = grp;
   }
+  // Problem-metadata reuse (reference: PMD_cache keyed by transposes, dimensions and
+  // operand locations, dgemm.cpp:342-380): a signature seen before skips the autotuner.
+  struct CachedPlan { paralia_report tuned; };
+  static std::map<std::string, CachedPlan> plan_cache;   // guarded by the call mutex
+  char sig[256];
+  snprintf(sig, sizeof(sig), "%s|%c%c|%lld,%lld,%lld|%d,%d,%d|T%lld|u%d:", func, g.ta, g.tb,
+           (long long)M, (long long)N, (long long)K, g.A.loc, g.B.loc, g.C.loc,
+           (long long)eff_ctl.T, eff_ctl.active_unit_num);
+  std::string key(sig);
+  for (int i = 0; i < eff_ctl.active_unit_num && i < PARALIA_MAX_UNITS; ++i)
+    key += std::to_string(eff_ctl.active_unit_id_list[i]) + ",";
+  key += model_db().from_disk ? model_db().dir : std::string("defaults");
   paralia_report tuned;
-  rc = autotune_gemm(mi_in, ngpu, &eff_ctl, &tuned);
-  if (rc != PARALIA_OK) { cleanup_pins(); return rc; }
+  bool reused = false;
+  auto hit = plan_cache.find(key);
+  if (hit != plan_cache.end() && !(eff_ctl.flags & PARALIA_FLAG_NO_METADATA_REUSE)) {
+    tuned = hit->second.tuned;
+    reused = true;
+  } else {
+    rc = autotune_gemm(mi_in, ngpu, &eff_ctl, &tuned);
+    if (rc != PARALIA_OK) { cleanup_pins(); return rc; }
+    if (plan_cache.size() >= 100) plan_cache.clear();   // reference: PROBLEM_MD_CACHE = 100
+    plan_cache[key] = CachedPlan{tuned};
+  }
   g.Tt = tuned.T;
   if (g.Tt % DG_BK && g.Tt < std::max(M, std::max(N, mi_in.K)))
     g.Tt = std::max<int64_t>(DG_BK, g.Tt - g.Tt % DG_BK);
@@ -829,6 +853,8 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
   rep->grid_d1 = d1; rep->grid_d2 = d2;
   rep->subkernel_num = g.Mt * g.Nt * kt_for_ids;
   rep->pin_ms = pin_ms;
+  rep->metadata_reused = reused ? 1 : 0;
+  rep->cache_limit = eff_ctl.cache_limit;
 
   g.units.assign(active, UnitState());
   g.ctile_owner.assign(g.Mt * g.Nt, -1);
@@ -885,12 +911,7 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
     int64_t need = 0;
     if (!u.a_native_ok) for (int64_t r = 0; r < g.Mt; ++r) if (rows[r]) need += g.Kt;
     if (!u.b_native_ok) for (int64_t c = 0; c < g.Nt; ++c) if (cols[c]) need += g.Kt;
-    // A home GPU may also hold tiles it forwards but never reads: bounded by one extra
-    // panel per operand; count what the home rule can send here.
-    if (g.peer_fetch && active > 1) {
-      if (g.A.loc == -1) need += 0;  // homes are always consumers of the tile row
-      if (g.B.loc == -1) need += 0;
-    }
+    // (a home GPU is always a consumer of the tiles it forwards, so it needs no extra blocks)
     if (!u.c_native) need += (int64_t)u.ctiles.size() * ((beta != (T)0) ? 2 : 1);
     // The slab is clamped by the caller's cache_limit and by what the GPU has left
     // (reference: min(cache_limit, free - 30 % of total), dgemm.cpp:53-54,80-87; here 90 %

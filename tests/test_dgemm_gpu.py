@@ -207,6 +207,21 @@ def test_dgemm_linearity_large(pl, orc):
         assert abs(dC1.view(n, n).T[i, j].item() - ref) <= tol(n) * n ** 0.5
 
 
+def test_dgemm_metadata_reuse(pl, orc):
+    # second call with the same signature skips the autotuner (reference: PMD_cache,
+    # dgemm.cpp:342-380) and gives the same bits
+    M, N, K = 640, 512, 384
+    A, B, C0, lda, ldb, ldc = _case(orc, "N", "T", M, N, K)
+    C1, C2, C3 = (C0.copy(order="F") for _ in range(3))
+    ctl = pl.make_ctl(T=128, units=[0])
+    pl.dgemm("N", "T", M, N, K, 1.5, A, lda, B, ldb, 0.25, C1, ldc, ctl=ctl)
+    r2 = pl.dgemm("N", "T", M, N, K, 1.5, A, lda, B, ldb, 0.25, C2, ldc, ctl=ctl)
+    r3 = pl.dgemm("N", "T", M, N, K, 1.5, A, lda, B, ldb, 0.25, C3, ldc,
+                  ctl=pl.make_ctl(T=128, units=[0], flags=pl.FLAG_NO_METADATA_REUSE))
+    assert r2.metadata_reused == 1 and r3.metadata_reused == 0
+    assert np.array_equal(C1, C2) and np.array_equal(C1, C3)
+
+
 def test_dgemm_k_zero_and_empty(pl, orc):
     M, N = 64, 48
     C = orc.matrix_f64(M, N, 44)
