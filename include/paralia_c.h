@@ -124,6 +124,15 @@ int PARALiA_sgemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K,
                   float beta, float* C, int64_t ldC, int locC,
                   const paralia_ctl* ctl, paralia_report* out);
 
+/* Replaces PARALiADgemv / PARALiADgemvControled (PARALiA.hpp:48-53,
+ * Library_scheduler/src/Functions/dgemv.cpp:288): y <- alpha*op(A)*x + beta*y, A is M x N
+ * column-major. ctl->T, if set, is the number of columns of A per tile. */
+int PARALiA_dgemv(char TransA, int64_t M, int64_t N, double alpha,
+                  const double* A, int64_t ldA, int locA,
+                  const double* x, int64_t incx, int locx,
+                  double beta, double* y, int64_t incy, int locy,
+                  const paralia_ctl* ctl, paralia_report* out);
+
 /* Replaces PARALiADaxpy / PARALiADaxpyControled (PARALiA.hpp:56-61,
  * Library_scheduler/src/Functions/daxpy.cpp:200-469): y <- alpha*x + y. */
 int PARALiA_daxpy(int64_t N, double alpha, const double* x, int64_t incx, int locx,

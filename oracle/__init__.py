@@ -59,6 +59,7 @@ def lib() -> C.CDLL:
                                          flt, vp, i64, i64]
         h.oracle_daxpy_tiled.argtypes = [i64, dbl, vp, i64, vp, i64, i64]
         h.oracle_ddot_tiled.argtypes = [i64, vp, i64, vp, i64, i64, C.POINTER(dbl), C.POINTER(dbl)]
+        h.oracle_dgemv.argtypes = [C.c_int, i64, i64, dbl, vp, i64, vp, i64, dbl, vp, i64]
         h.oracle_tile_slowdowns.argtypes = [i64, i64, i64, i64, C.c_int, C.POINTER(dbl)]
         h.oracle_optimize_tile.argtypes = [i64, i64, i64, C.c_int, i64, C.POINTER(dbl)]
         h.oracle_optimize_tile.restype = i64
@@ -127,6 +128,13 @@ def ddot_tiled(N, x, incx, y, incy, T, result: float = 0.0):
     return res.value, mag.value
 
 
+def dgemv(ta, M, N, alpha, A, lda, x, incx, beta, y, incy) -> None:
+    """In place on y."""
+    rc = lib().oracle_dgemv(_t(ta), M, N, alpha, A.ctypes.data, lda, x.ctypes.data, incx, beta,
+                            y.ctypes.data, incy)
+    assert rc == 0
+
+
 def tile_slowdowns(D1, D2, D3, T, units) -> list[float]:
     sl = (C.c_double * 6)()
     lib().oracle_tile_slowdowns(D1, D2, D3, T, units, sl)
@@ -167,6 +175,11 @@ def openblas_sgemm(ta, tb, alpha, A, B, beta, Cm) -> np.ndarray:
     from scipy.linalg import blas
     return blas.sgemm(alpha, A, B, beta=beta, c=Cm, trans_a=_t(ta), trans_b=_t(tb),
                       overwrite_c=False)
+
+
+def openblas_dgemv(ta, alpha, A, x, beta, y) -> np.ndarray:
+    from scipy.linalg import blas
+    return blas.dgemv(alpha, A, x, beta=beta, y=y.copy(), trans=_t(ta))
 
 
 def openblas_daxpy(alpha, x, y) -> np.ndarray:

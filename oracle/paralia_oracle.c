@@ -332,3 +332,23 @@ int oracle_distribute_2d(int units, int Mt, int Nt, int Kt, int32_t* owner, int3
   free(num);
   return active;
 }
+
+/* ---- DGEMV: y <- alpha*op(A)*x + beta*y, A is M x N column-major
+ * (Library_scheduler/include/PARALiA.hpp:48-53, Library_scheduler/src/Functions/dgemv.cpp:288).
+ * Sums are taken in long double so that the oracle is at least as accurate as any
+ * summation order of the GPU path. */
+int oracle_dgemv(int trans, int64_t M, int64_t N, double alpha, const double* A, int64_t lda,
+                 const double* x, int64_t incx, double beta, double* y, int64_t incy) {
+  if (M < 0 || N < 0) return 1;
+  const int64_t out_len = trans ? N : M, in_len = trans ? M : N;
+  for (int64_t o = 0; o < out_len; ++o) {
+    long double s = 0.0L;
+    for (int64_t i = 0; i < in_len; ++i) {
+      const double a = trans ? A[i + o * lda] : A[o + i * lda];
+      s += (long double)a * (long double)x[i * incx];
+    }
+    double* yo = &y[o * incy];
+    *yo = (beta == 0.0) ? (double)(alpha * s) : (double)(alpha * s + (long double)beta * (*yo));
+  }
+  return 0;
+}

@@ -119,6 +119,8 @@ SIGNATURES = {
                                 C.c_int, _dbl, _vp, _i64, C.c_int, _ctl_p, _rep_p]),
     "PARALiA_sgemm": (C.c_int, [_chr, _chr, _i64, _i64, _i64, _flt, _vp, _i64, C.c_int, _vp, _i64,
                                 C.c_int, _flt, _vp, _i64, C.c_int, _ctl_p, _rep_p]),
+    "PARALiA_dgemv": (C.c_int, [_chr, _i64, _i64, _dbl, _vp, _i64, C.c_int, _vp, _i64, C.c_int, _dbl,
+                                _vp, _i64, C.c_int, _ctl_p, _rep_p]),
     "PARALiA_daxpy": (C.c_int, [_i64, _dbl, _vp, _i64, C.c_int, _vp, _i64, C.c_int, _ctl_p, _rep_p]),
     "PARALiA_ddot": (C.c_int, [_i64, _vp, _i64, C.c_int, _vp, _i64, C.c_int, C.POINTER(_dbl),
                                _ctl_p, _rep_p]),
@@ -287,6 +289,16 @@ def sgemm(TransA, TransB, M, N, K, alpha, A, ldA, B, ldB, beta, Cm, ldC,
     rep = Report()
     _check(lib().PARALiA_sgemm(_c(TransA), _c(TransB), M, N, K, alpha, _ptr(A), ldA, locA,
                                _ptr(B), ldB, locB, beta, _ptr(Cm), ldC, locC,
+                               C.byref(ctl) if ctl is not None else None, C.byref(rep)))
+    return rep
+
+
+def dgemv(TransA, M, N, alpha, A, ldA, x, incx, beta, y, incy, locA=LOC_AUTO, locx=LOC_AUTO,
+          locy=LOC_AUTO, ctl: Ctl | None = None) -> Report:
+    """Reference: PARALiADgemv (dgemv.cpp:288). ctl.T = columns of A per tile."""
+    rep = Report()
+    _check(lib().PARALiA_dgemv(_c(TransA), M, N, alpha, _ptr(A), ldA, locA, _ptr(x), incx, locx,
+                               beta, _ptr(y), incy, locy,
                                C.byref(ctl) if ctl is not None else None, C.byref(rep)))
     return rep
 

@@ -85,6 +85,12 @@ int PARALiA_sgemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, flo
                     ctl, out);
 }
 
+int PARALiA_dgemv(char TransA, int64_t M, int64_t N, double alpha, const double* A, int64_t ldA,
+                  int locA, const double* x, int64_t incx, int locx, double beta, double* y,
+                  int64_t incy, int locy, const paralia_ctl* ctl, paralia_report* out) {
+  return exec_dgemv(TransA, M, N, alpha, A, ldA, locA, x, incx, locx, beta, y, incy, locy, ctl, out);
+}
+
 int PARALiA_daxpy(int64_t N, double alpha, const double* x, int64_t incx, int locx, double* y,
                   int64_t incy, int locy, const paralia_ctl* ctl, paralia_report* out) {
   return exec_daxpy(N, alpha, x, incx, locx, y, incy, locy, ctl, out);

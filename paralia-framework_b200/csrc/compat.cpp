@@ -157,6 +157,20 @@ ATC_p PARALiASgemm(char TransA, char TransB, long int M, long int N, long int K,
   return PARALiASgemmControled(TransA, TransB, M, N, K, alpha, A, ldA, B, ldB, beta, C, ldC, NULL);
 }
 
+ATC_p PARALiADgemvControled(char TransA, long int M, long int N, double alpha, double* A,
+                            long int ldA, double* x, long int incx, double beta, double* y,
+                            long int incy, ATC_p predef) {
+  paralia_ctl c;
+  paralia_report r;
+  int rc = PARALiA_dgemv(TransA, M, N, alpha, A, ldA, PARALIA_LOC_AUTO, x, incx, PARALIA_LOC_AUTO,
+                         beta, y, incy, PARALIA_LOC_AUTO, to_ctl(predef, &c), &r);
+  return from_report(rc, r, "PARALiADgemv");
+}
+ATC_p PARALiADgemv(char TransA, long int M, long int N, double alpha, double* A, long int ldA,
+                   double* x, long int incx, double beta, double* y, long int incy) {
+  return PARALiADgemvControled(TransA, M, N, alpha, A, ldA, x, incx, beta, y, incy, NULL);
+}
+
 ATC_p PARALiADaxpyControled(long int N, double alpha, double* x, long int incx, double* y,
                             long int incy, ATC_p predef) {
   paralia_ctl c;

@@ -29,6 +29,10 @@ int exec_tile_sgemm(int dev, void* stream, char ta, char tb, int64_t M, int64_t 
                     float alpha, const float* A, int64_t ldA, const float* B, int64_t ldB,
                     float beta, float* C, int64_t ldC);
 
+int exec_dgemv(char TransA, int64_t M, int64_t N, double alpha, const double* A, int64_t ldA,
+               int locA, const double* x, int64_t incx, int locx, double beta, double* y,
+               int64_t incy, int locy, const paralia_ctl* ctl, paralia_report* out);
+
 int exec_daxpy(int64_t N, double alpha, const double* x, int64_t incx, int locx, double* y,
                int64_t incy, int locy, const paralia_ctl* ctl, paralia_report* out);
 

@@ -7,6 +7,7 @@ Level 3 (same argument order as the reference's runners)::
 
     python runner.py dgemm|sgemm active_unit_num dev_ids T cache_limit TransA TransB alpha beta M N K locA locB locC outloc
     python runner.py daxpy|ddot  active_unit_num dev_ids T cache_limit alpha N incx incy locx locy
+    python runner.py dgemv       active_unit_num dev_ids T cache_limit TransA alpha beta M N incx incy locA locx locy
 
 ``active_unit_num < 0`` = autotuned unit set; ``dev_ids`` is the reference's decimal mask
 (``0101`` = GPUs 0 and 2); ``T <= 0`` = autotuned tile; locations: -1 pinned host, >= 0 GPU.
@@ -217,9 +218,56 @@ def run_level1(pl, a, routine: str) -> dict:
     return out
 
 
+def run_dgemv(pl, a) -> dict:
+    M, N = a.M, a.N
+    in_len, out_len = (M, N) if a.TransA == "T" else (N, M)
+    specs = ((M * N, 42, a.locA), (1 + (in_len - 1) * a.incx, 43, a.locx),
+             (1 + (out_len - 1) * a.incy, 44, a.locy))
+    bufs = []
+    for (cnt, seed, loc) in specs:
+        p = pl.malloc(cnt * 8, loc)
+        if loc >= 0:
+            pl.fill_f64(p, cnt, seed, 0, loc)
+        else:
+            tmp = pl.malloc(cnt * 8, 0)
+            pl.fill_f64(tmp, cnt, seed, 0, 0)
+            pl.memcpy(p, -1, tmp, 0, cnt * 8)
+            pl.free(tmp, 0)
+        bufs.append(p)
+    A, x, y = bufs
+    ctl = pl.make_ctl(T=max(a.T, 0), units=parse_mask(a.active_unit_num, a.dev_ids))
+    call = lambda: pl.dgemv(a.TransA, M, N, a.alpha, A, M, x, a.incx, a.beta, y, a.incy,
+                            locA=a.locA, locx=a.locx, locy=a.locy, ctl=ctl)
+    t0 = time.perf_counter()
+    rep = call()
+    first = time.perf_counter() - t0
+    for _ in range(10 if a.warmup < 0 else a.warmup):
+        call()
+    times, dev_ms = [], []
+    for _ in range(a.iters):
+        t0 = time.perf_counter()
+        rep = call()
+        times.append(time.perf_counter() - t0)
+        dev_ms.append(rep.device_ms)
+        if a.log:
+            with open(a.log, "a") as f:   # level-2 row of the reference (testing.cpp StoreLogLvl2)
+                f.write(f"{csv_control(rep)}, {a.TransA},{a.alpha:.5f},{a.beta:.5f},{M},{N},{a.incx},"
+                        f"{a.incy},{a.locA},{a.locx},{a.locy},{a.locy}, {times[-1]:e},{rep.pred_t:e},"
+                        f"{rep.pred_J:e}\n")
+    nbytes = 8.0 * M * N
+    out = {"routine": "dgemv", "control": csv_control(rep), "first_s": first,
+           "avg_s": sum(times) / len(times), "min_s": min(times),
+           "gbs_avg": nbytes / (sum(times) / len(times)) / 1e9,
+           "gbs_device_best": nbytes / (min(dev_ms) * 1e-3) / 1e9,
+           "h2d_bytes": rep.h2d_bytes, "d2h_bytes": rep.d2h_bytes, "launches": rep.kernel_launches}
+    for p, loc in zip(bufs, (a.locA, a.locx, a.locy)):
+        pl.free(p, loc)
+    return out
+
+
 def main(argv=None) -> dict:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
-    ap.add_argument("routine", choices=["dgemm", "sgemm", "daxpy", "ddot"])
+    ap.add_argument("routine", choices=["dgemm", "sgemm", "dgemv", "daxpy", "ddot"])
     ap.add_argument("active_unit_num", type=int)
     ap.add_argument("dev_ids")
     ap.add_argument("T", type=int)
@@ -241,6 +289,14 @@ def main(argv=None) -> dict:
         a.M, a.N, a.K = int(r[4]), int(r[5]), int(r[6])
         a.locA, a.locB, a.locC, a.outloc = (int(v) for v in r[7:11])
         out = run_level3(pl, a, a.routine)
+    elif a.routine == "dgemv":
+        if len(r) != 10:
+            raise SystemExit("level 2 needs: TransA alpha beta M N incx incy locA locx locy")
+        a.TransA = r[0].upper()
+        a.alpha, a.beta = float(r[1]), float(r[2])
+        a.M, a.N, a.incx, a.incy = (int(v) for v in r[3:7])
+        a.locA, a.locx, a.locy = (int(v) for v in r[7:10])
+        out = run_dgemv(pl, a)
     else:
         if len(r) != 6:
             raise SystemExit("level 1 needs: alpha N incx incy locx locy")

@@ -117,3 +117,16 @@ def test_tile_score_worked_example(orc):
     assert orc.tile_slowdowns(32768, 32768, 32768, 2048, 8)[0] == pytest.approx(2 / 512)
     T, sl = orc.optimize_tile(32768, 32768, 32768, 8)
     assert T == 2048 and sl[0] == pytest.approx(2 / 512)
+
+
+@pytest.mark.parametrize("ta", ["N", "T"])
+@pytest.mark.parametrize("dims", [(64, 48), (37, 53), (1, 70), (70, 1), (300, 200)])
+def test_dgemv_oracle_vs_openblas_live(orc, ta, dims):
+    M, N = dims
+    A = orc.matrix_f64(M, N, 42, M + 3)
+    in_len, out_len = (M, N) if ta == "T" else (N, M)
+    x = orc.uniform_f64(in_len, 43)
+    y = orc.uniform_f64(out_len, 44)
+    want = orc.openblas_dgemv(ta, 1.23, A[:M, :], x, 0.9876, y)
+    orc.dgemv(ta, M, N, 1.23, A, M + 3, x, 1, 0.9876, y, 1)
+    assert orc.normwise_rel_err(y, want) <= 8 * in_len * EPS64
