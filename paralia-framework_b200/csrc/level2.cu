@@ -36,7 +36,7 @@ dgemv_n_partial_kernel(int rows, int cols, const double* __restrict__ A, int64_t
     __syncthreads();
     if (m + 1 < rows && vec_ok) {
       const double* col = A + m + (int64_t)n0 * lda;
-#pragma unroll 4
+#pragma unroll 8
       for (int i = 0; i < cnt; ++i) {
         const double2 a = *reinterpret_cast<const double2*>(col + (int64_t)i * lda);
         acc0 = fma(a.x, xs[i], acc0);

@@ -135,10 +135,13 @@ int exec_dgemv(char TransA, int64_t M, int64_t N, double alpha, const double* A,
     units[ui].o_hi = std::min(out_len, lo * 2);
     max_run = std::max(max_run, units[ui].o_hi - units[ui].o_lo);
   }
-  // columns per tile: about 64 MiB of A per tile, a multiple of 64 columns
+  // columns per tile: about 64 MiB of A per tile, a multiple of 64 columns; a panel that
+  // already lives on its (only) GPU is not staged at all and runs as one tile
   const int64_t panel_rows = trans ? M : max_run;
   int64_t Tc = (ctl && ctl->T > 0) ? ctl->T : 0;
-  if (Tc <= 0) {
+  if (Tc <= 0 && U == 1 && lA == devs[0]) {
+    Tc = ceil_div(trans ? max_run : N, 64) * 64;
+  } else if (Tc <= 0) {
     Tc = (64ll << 20) / std::max<int64_t>(8, panel_rows * 8);
     Tc = std::max<int64_t>(64, Tc / 64 * 64);
   }
