@@ -410,6 +410,16 @@ double predict_gemm(const GemmModelInput& in, int64_t T, const std::vector<int>&
     p.t_extra = extra;
     p.t_total = std::max(std::max(p.t_exec, p.t_recv), std::max(p.t_send, p.t_extra));
     p.t_total *= (1.0 + (sl ? sl[0] : 0.0));
+    // What the overlap cannot hide: the first A and B (and C) tiles have to arrive before
+    // the first tile product starts, and the last C tile leaves after the last one ends.
+    // (The reference folds this into its tile-size slowdown constants; with measured links
+    // it is cheaper to state it.)
+    const double tile_bytes = (double)Tb * Tb * in.esz;
+    double fill = 0.0;
+    if (in.locA != dev) fill += link_time(dev, in.locA, tile_bytes);
+    if (in.locB != dev) fill += link_time(dev, in.locB, tile_bytes);
+    if (in.locC != dev) fill += link_time(dev, in.locC, tile_bytes * inC) + link_time(in.locC, dev, tile_bytes);
+    p.t_total += fill;
     worst = std::max(worst, p.t_total);
     if (per_unit) per_unit->push_back(p);
   }

@@ -410,30 +410,46 @@ int PARALiA_bench_dmma_peak(int dev, int shape, int iters, double* tflops) {
 
 int PARALiA_bench_tile_dgemm(int dev, char TransA, char TransB, int64_t T, int reps,
                              double* mean_s) {
+  // The tile time the model needs is the one the executor sees: tiles of different C
+  // accumulators run on several exec streams at once, so the partial last wave of one tile
+  // is filled by the next. `reps` tiles are therefore spread round-robin over up to four
+  // streams (one C per stream) and the mean is total time / reps; reps = 1 times one tile
+  // alone, as the reference's microbenchmark does (dgemm_microbench.cu:125-187).
   if (!mean_s || reps <= 0 || T <= 0) return fail(PARALIA_ERR_INVALID_ARG, "bad bench arguments");
   DeviceGuard guard;
   PL_TRY(setup_device(dev));
+  DeviceCtx& dc = Runtime::get().dev(dev);
+  const int S = std::min(reps, 4);
   const size_t n = (size_t)T * T;
   double *A = nullptr, *B = nullptr, *C = nullptr;
   PL_CUDA(cudaMalloc(&A, n * 8));
   PL_CUDA(cudaMalloc(&B, n * 8));
-  PL_CUDA(cudaMalloc(&C, n * 8));
+  PL_CUDA(cudaMalloc(&C, n * 8 * S));
   PL_CUDA(launch_fill_f64(A, n, 42, 0, nullptr));
   PL_CUDA(launch_fill_f64(B, n, 43, 0, nullptr));
-  PL_CUDA(launch_fill_f64(C, n, 44, 0, nullptr));
-  cudaEvent_t e0, e1;
+  PL_CUDA(launch_fill_f64(C, n * S, 44, 0, nullptr));
+  PL_CUDA(cudaDeviceSynchronize());
+  cudaEvent_t e0, e1, join[4] = {nullptr, nullptr, nullptr, nullptr};
   PL_CUDA(cudaEventCreate(&e0));
   PL_CUDA(cudaEventCreate(&e1));
+  for (int s = 1; s < S; ++s) PL_CUDA(cudaEventCreateWithFlags(&join[s], cudaEventDisableTiming));
   int rc = PARALIA_OK;
   for (int i = 0; i < 2 && rc == PARALIA_OK; ++i)
-    rc = PARALiA_tile_dgemm(dev, nullptr, TransA, TransB, T, T, T, 1.0, A, T, B, T, 0.5, C, T);
+    rc = PARALiA_tile_dgemm(dev, dc.exec[0], TransA, TransB, T, T, T, 1.0, A, T, B, T, 0.5, C, T);
   if (rc == PARALIA_OK) {
     PL_CUDA(cudaSetDevice(dev));
-    PL_CUDA(cudaEventRecord(e0, nullptr));
+    PL_CUDA(cudaDeviceSynchronize());
+    PL_CUDA(cudaEventRecord(e0, dc.exec[0]));
+    for (int s = 1; s < S; ++s) PL_CUDA(cudaStreamWaitEvent(dc.exec[s], e0, 0));
     for (int i = 0; i < reps && rc == PARALIA_OK; ++i)
-      rc = PARALiA_tile_dgemm(dev, nullptr, TransA, TransB, T, T, T, 1.0, A, T, B, T, 0.5, C, T);
+      rc = PARALiA_tile_dgemm(dev, dc.exec[i % S], TransA, TransB, T, T, T, 1.0, A, T, B, T, 0.5,
+                              C + (size_t)(i % S) * n, T);
     PL_CUDA(cudaSetDevice(dev));
-    PL_CUDA(cudaEventRecord(e1, nullptr));
+    for (int s = 1; s < S; ++s) {
+      PL_CUDA(cudaEventRecord(join[s], dc.exec[s]));
+      PL_CUDA(cudaStreamWaitEvent(dc.exec[0], join[s], 0));
+    }
+    PL_CUDA(cudaEventRecord(e1, dc.exec[0]));
     PL_CUDA(cudaEventSynchronize(e1));
     float ms = 0.f;
     PL_CUDA(cudaEventElapsedTime(&ms, e0, e1));
@@ -441,6 +457,7 @@ int PARALiA_bench_tile_dgemm(int dev, char TransA, char TransB, int64_t T, int r
   }
   cudaEventDestroy(e0);
   cudaEventDestroy(e1);
+  for (int s = 1; s < S; ++s) cudaEventDestroy(join[s]);
   cudaFree(A);
   cudaFree(B);
   cudaFree(C);

@@ -92,7 +92,7 @@ def build_exec(pl, db: Path, dev: int, quick: bool):
             lines = []
             for T in tile_sizes(quick):
                 mean, err, n, bt = sample_until_confident(
-                    lambda: pl.bench_tile_dgemm(dev, ta, tb, T, 1 if T >= 2048 else 4))
+                    lambda: pl.bench_tile_dgemm(dev, ta, tb, T, 8))   # 8 tiles over 4 streams: in-pipeline time
                 lines.append(f"{T},{T},{T}, {mean:e},0,0,{err:e},{n},{bt:e}")
                 rows["Dgemm"].append((ta, tb, T, mean, err, n, bt))
             (raw / f"cublasDgemm_dev-{dev}_TransA-{ta}_TransB-{tb}_{VERSION}.log").write_text(

@@ -8,6 +8,8 @@ Level 3 (same argument order as the reference's runners)::
     python runner.py dgemm|sgemm active_unit_num dev_ids T cache_limit TransA TransB alpha beta M N K locA locB locC outloc
     python runner.py daxpy|ddot  active_unit_num dev_ids T cache_limit alpha N incx incy locx locy
     python runner.py dgemv       active_unit_num dev_ids T cache_limit TransA alpha beta M N incx incy locA locx locy
+    python runner.py dgemm_predict|sgemm_predict  (level-3 arguments)   # autotuner only, nothing runs on a GPU stream
+    python runner.py cublasxt_dgemm|cublasxt_sgemm (level-3 arguments)  # the reference's comparator, same protocol
 
 ``active_unit_num < 0`` = autotuned unit set; ``dev_ids`` is the reference's decimal mask
 (``0101`` = GPUs 0 and 2); ``T <= 0`` = autotuned tile; locations: -1 pinned host, >= 0 GPU.
@@ -65,7 +67,7 @@ def run_level3(pl, a, routine: str) -> dict:
     import numpy as np
     esz = 8 if routine == "dgemm" else 4
     fill = pl.fill_f64 if esz == 8 else pl.fill_f32
-    gemm = pl.dgemm if esz == 8 else pl.sgemm
+    sys.path.insert(0, str(PKG_DIR))
     M, N, K = a.M, a.N, a.K
     ar, ac = (K, M) if a.TransA == "T" else (M, K)
     br, bc = (N, K) if a.TransB == "T" else (K, N)
@@ -84,9 +86,23 @@ def run_level3(pl, a, routine: str) -> dict:
     A, B, C = bufs
     units = parse_mask(a.active_unit_num, a.dev_ids)
     ctl = pl.make_ctl(T=max(a.T, 0), units=units, cache_limit=max(a.cache_limit, 0))
-    call = lambda: gemm(a.TransA, a.TransB, M, N, K, a.alpha, A, ar, B, br, a.beta, C, M,
-                        locA=a.locA, locB=a.locB, locC=a.locC, ctl=ctl)
-    out = {"routine": routine}
+    if getattr(a, "comparator", False):
+        # whole-problem cuBLASXt as the reference runs it (cuBLASXt_dgemm_runner): block
+        # dimension T (default min(M,N,K)/2 capped at 10000), device list from the mask
+        import comparators
+        devs = units if units else list(range(pl.device_count()))
+        rep_like = pl.autotune_gemm(esz, a.TransA, a.TransB, M, N, K, a.locA, a.locB, a.locC, ctl)
+
+        def call():
+            comparators.cublasxt_gemm(esz, a.TransA, a.TransB, M, N, K, a.alpha, A, ar, B, br,
+                                      a.beta, C, M, T=a.T, dev_ids=devs, pinning=False)
+            rep_like.device_ms = float("nan")
+            return rep_like
+    else:
+        gemm = pl.dgemm if esz == 8 else pl.sgemm
+        call = lambda: gemm(a.TransA, a.TransB, M, N, K, a.alpha, A, ar, B, br, a.beta, C, M,
+                            locA=a.locA, locB=a.locB, locC=a.locC, ctl=ctl)
+    out = {"routine": ("cublasxt_" if getattr(a, "comparator", False) else "") + routine}
     if a.validate:
         out["validation"] = validate_level3(pl, a, routine, A, B, C, ar, br, call)
         fill_c = C
@@ -121,6 +137,29 @@ def run_level3(pl, a, routine: str) -> dict:
     for p, loc in zip(bufs, (a.locA, a.locB, a.locC)):
         pl.free(p, loc)
     return out
+
+
+def run_predict(pl, a, routine: str) -> dict:
+    """Autotune-only run: the model's choice of tile, unit set and its time prediction for a
+    problem, without moving or computing anything (reference:
+    ``Benchmarking/CuCuBLAS/src/PARALia/dgemm_predictor.cpp:16-93``)."""
+    esz = 8 if routine.startswith("d") else 4
+    units = parse_mask(a.active_unit_num, a.dev_ids)
+    ctl = pl.make_ctl(T=max(a.T, 0), units=units, cache_limit=max(a.cache_limit, 0))
+    t0 = time.perf_counter()
+    rep = pl.autotune_gemm(esz, a.TransA, a.TransB, a.M, a.N, a.K, a.locA, a.locB, a.locC, ctl)
+    t_auto = time.perf_counter() - t0
+    if a.log:
+        with open(a.log, "a") as f:
+            f.write(f"{csv_control(rep)}, {a.TransA},{a.TransB},{a.alpha:.5f},{a.beta:.5f},"
+                    f"{a.M},{a.N},{a.K},{a.locA},{a.locB},{a.locC},{a.outloc}, "
+                    f"{t_auto:e},{rep.pred_t:e},{rep.pred_J:e}\n")
+    n = max(rep.active_unit_num, 0)
+    return {"routine": routine, "control": csv_control(rep), "t_autotune_ms": t_auto * 1e3,
+            "T": rep.T, "units": [int(rep.active_unit_id_list[i]) for i in range(n)],
+            "grid": [rep.grid_d1, rep.grid_d2], "subkernels": rep.subkernel_num,
+            "pred_t": rep.pred_t, "pred_tflops": 2.0 * a.M * a.N * a.K / max(rep.pred_t, 1e-30) / 1e12,
+            "T_slowdowns": [float(v) for v in rep.T_slowdowns]}
 
 
 def validate_level3(pl, a, routine, A, B, C, ar, br, call) -> dict:
@@ -267,7 +306,7 @@ def run_dgemv(pl, a) -> dict:
 
 def main(argv=None) -> dict:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
-    ap.add_argument("routine", choices=["dgemm", "sgemm", "dgemv", "daxpy", "ddot"])
+    ap.add_argument("routine", choices=["dgemm", "sgemm", "dgemv", "daxpy", "ddot", "dgemm_predict", "sgemm_predict", "cublasxt_dgemm", "cublasxt_sgemm"])
     ap.add_argument("active_unit_num", type=int)
     ap.add_argument("dev_ids")
     ap.add_argument("T", type=int)
@@ -281,14 +320,17 @@ def main(argv=None) -> dict:
     r = a.rest
     pl = _pkg()
     pl.init()
-    if a.routine in ("dgemm", "sgemm"):
+    a.comparator = a.routine.startswith("cublasxt_")
+    if a.comparator:
+        a.routine = a.routine[len("cublasxt_"):]
+    if a.routine in ("dgemm", "sgemm", "dgemm_predict", "sgemm_predict"):
         if len(r) != 11:
             raise SystemExit("level 3 needs: TransA TransB alpha beta M N K locA locB locC outloc")
         a.TransA, a.TransB = r[0].upper(), r[1].upper()
         a.alpha, a.beta = float(r[2]), float(r[3])
         a.M, a.N, a.K = int(r[4]), int(r[5]), int(r[6])
         a.locA, a.locB, a.locC, a.outloc = (int(v) for v in r[7:11])
-        out = run_level3(pl, a, a.routine)
+        out = run_predict(pl, a, a.routine) if a.routine.endswith("_predict") else run_level3(pl, a, a.routine)
     elif a.routine == "dgemv":
         if len(r) != 10:
             raise SystemExit("level 2 needs: TransA alpha beta M N incx incy locA locx locy")
