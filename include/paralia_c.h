@@ -107,6 +107,12 @@ const char* PARALiA_last_error(void);
 int PARALiA_dev_cache_free(int loc);
 
 /* ---- the four routines of the hot path -------------------------------------------- */
+/* Stream semantics of the whole-problem routines below: they run on the library's own
+ * (non-blocking) streams and are blocking calls, so everything they wrote is visible when
+ * they return. On entry they wait for work the caller already queued on the legacy default
+ * stream of every GPU that holds an operand or takes part (a kernel or copy that produced an
+ * operand there); work queued on other streams has to be synchronised by the caller. The
+ * PARALiA_tile_* entry points further down run on the stream the caller passes. */
 /* Replaces PARALiADgemm / PARALiADgemmControled (PARALiA.hpp:33-38,
  * dgemm.cpp:318-705): C <- alpha*op(A)*op(B) + beta*C, FP64. Blocking: returns after C
  * is completely written (dgemm.cpp:596-597). */

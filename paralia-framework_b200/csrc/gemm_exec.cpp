@@ -996,6 +996,16 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
   rep->plan_ms = wall_ms() - t_plan0 - alloc_ms;
 
   // ------------------------------ enqueue ------------------------------
+  {
+    // operands the caller produced on the default stream of a GPU are ready before we read
+    std::vector<int> op_devs = {g.A.loc, g.B.loc, g.C.loc}, unit_devs;
+    for (int ui = 0; ui < active; ++ui) {
+      op_devs.push_back(g.units[ui].dev);
+      unit_devs.push_back(g.units[ui].dev);
+    }
+    const int orc = rt.order_after_caller(op_devs, unit_devs);
+    if (orc != PARALIA_OK) return fail_out(orc);
+  }
   for (int ui = 0; ui < active; ++ui) {
     UnitState& u = g.units[ui];
     DeviceCtx& dc = rt.dev(u.dev);

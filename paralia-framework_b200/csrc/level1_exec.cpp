@@ -181,6 +181,12 @@ int run_level1(bool is_dot, int64_t N, double alpha, const double* x, int64_t in
   rep->alloc_ms = alloc_ms;
   rep->plan_ms = wall_ms() - t_plan0 - alloc_ms;
 
+  {
+    std::vector<int> op_devs = {vx.loc, vy.loc}, unit_devs;
+    for (const L1Unit& u : units) { op_devs.push_back(u.dev); unit_devs.push_back(u.dev); }
+    rc = rt.order_after_caller(op_devs, unit_devs);
+    if (rc != PARALIA_OK) { cleanup(); return rc; }
+  }
   // ---- enqueue, round-robin over the GPUs one tile at a time
   for (int ui = 0; ui < U; ++ui) {
     DeviceCtx& dc = rt.dev(units[ui].dev);

@@ -190,6 +190,12 @@ int exec_dgemv(char TransA, int64_t M, int64_t N, double alpha, const double* A,
   rep->alloc_ms = alloc_ms;
   rep->plan_ms = wall_ms() - t_plan0 - alloc_ms;
 
+  {
+    std::vector<int> op_devs = {lA, lx, ly}, unit_devs;
+    for (const GvUnit& u : units) { op_devs.push_back(u.dev); unit_devs.push_back(u.dev); }
+    rc = rt.order_after_caller(op_devs, unit_devs);
+    if (rc != PARALIA_OK) { cleanup(); return rc; }
+  }
   // ---- enqueue: per GPU x, its run of y, then the column tiles of its panel
   auto enqueue_unit = [&](int ui) -> int {
     GvUnit& u = units[ui];

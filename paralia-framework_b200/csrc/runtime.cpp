@@ -1,3 +1,4 @@
+#include <algorithm>
 #include "runtime.hpp"
 
 #include <chrono>
@@ -57,6 +58,24 @@ int Runtime::init() {
   return PARALIA_OK;
 }
 
+int Runtime::order_after_caller(const std::vector<int>& devs, const std::vector<int>& units) {
+  std::vector<int> marked;
+  for (int d : devs) {
+    if (d < 0 || d >= ndev_) continue;   // host operands have no stream to join
+    if (std::find(marked.begin(), marked.end(), d) != marked.end()) continue;
+    PL_TRY(ensure_device(d));
+    PL_CUDA(cudaSetDevice(d));
+    PL_CUDA(cudaEventRecord(devs_[d].caller_ready, cudaStreamLegacy));
+    marked.push_back(d);
+  }
+  for (int u : units) {
+    PL_TRY(ensure_device(u));
+    PL_CUDA(cudaSetDevice(u));
+    for (int d : marked) PL_CUDA(cudaStreamWaitEvent(devs_[u].h2d, devs_[d].caller_ready, 0));
+  }
+  return PARALIA_OK;
+}
+
 int Runtime::ensure_device(int d) {
   if (d < 0 || d >= ndev_) return fail(PARALIA_ERR_INVALID_ARG, "GPU id %d out of range", d);
   DeviceCtx& c = devs_[d];
@@ -72,6 +91,7 @@ int Runtime::ensure_device(int d) {
     PL_CUDA(cudaEventCreateWithFlags(&c.stage_free[i], cudaEventDisableTiming));
   PL_CUDA(cudaEventCreate(&c.t_begin));
   PL_CUDA(cudaEventCreate(&c.t_end));
+  PL_CUDA(cudaEventCreateWithFlags(&c.caller_ready, cudaEventDisableTiming));
   PL_CUDA(cudaMalloc(&c.status_dev, sizeof(int)));
   PL_CUDA(cudaMemset(c.status_dev, 0, sizeof(int)));
   PL_CUDA(dgemm_tile_configure());
@@ -234,6 +254,7 @@ int Runtime::finalize() {
       for (int i = 0; i < DeviceCtx::STAGE_SLOTS; ++i) cudaEventDestroy(c.stage_free[i]);
       for (int i = 0; i < MAX_EXEC_STREAMS; ++i) cudaStreamDestroy(c.exec[i]);
       cudaEventDestroy(c.t_begin);
+      if (c.caller_ready) cudaEventDestroy(c.caller_ready);
       cudaEventDestroy(c.t_end);
     }
   }

@@ -53,6 +53,7 @@ struct DeviceCtx {
   bool stage_used[STAGE_SLOTS] = {};
   int stage_next = 0;
   cudaEvent_t t_begin = nullptr, t_end = nullptr;  // timing events
+  cudaEvent_t caller_ready = nullptr;  // marks the caller's default-stream work at call entry
   // Tile cache: one allocation cut into equal blocks (reference: Buffer / CBlock,
   // sized by ManageCachesDgemm, Library_scheduler/src/Functions/dgemm.cpp:23-121).
   void* slab = nullptr;
@@ -91,6 +92,12 @@ class Runtime {
   void release_events(int d) { devs_[d].events_used = 0; }
   // Read and clear GPU d's kernel status word (synchronises the device).
   int check_status(int d);
+  // Order a call after what the caller already queued on the legacy default stream of the
+  // GPUs in `devs` (a fill, a copy or a kernel that produces an operand): the library's
+  // streams are non-blocking and would not see that work otherwise. The h2d stream of every
+  // GPU in `units` waits; the call's start event is recorded on that stream afterwards.
+  // Work on other streams of the caller has to be synchronised by the caller.
+  int order_after_caller(const std::vector<int>& devs, const std::vector<int>& units);
   std::mutex& call_mutex() { return call_mutex_; }
 
  private:

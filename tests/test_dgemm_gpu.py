@@ -304,3 +304,23 @@ def test_fill_same_bits_on_host_and_device(pl, orc):
     d32 = torch.empty(n, dtype=torch.float32, device="cuda:0")
     pl.fill_f32(d32, n, 43, 0, 0)
     assert np.array_equal(d32.cpu().numpy(), orc.uniform_f32(n, 43))
+
+
+def test_call_waits_for_default_stream_work(pl, orc):
+    # operands produced by still-running work on the default stream (torch's stream): the
+    # call has to order itself after it although its own streams are non-blocking
+    import torch
+    M = N = K = 1024
+    A, B, C, lda, ldb, ldc = _case(orc, "N", "N", M, N, K)
+    want = C.copy(order="F")
+    orc.dgemm_tiled("N", "N", M, N, K, 1.0, A, lda, B, ldb, 1.0, want, ldc, 512)
+    dA, dB, dC0 = _dev(A), _dev(B), _dev(C)
+    big = torch.empty(1 << 28, dtype=torch.float64, device="cuda:0")   # 2 GiB of queued work
+    dC = torch.empty_like(dC0)
+    torch.cuda.synchronize()
+    for _ in range(8):
+        big.add_(1.0)
+    dC.copy_(dC0)                       # C becomes valid only after the queue above drains
+    pl.dgemm("N", "N", M, N, K, 1.0, dA, lda, dB, ldb, 1.0, dC, ldc, locA=0, locB=0, locC=0,
+             ctl=pl.make_ctl(T=512, units=[0]))
+    assert orc.normwise_rel_err(_host(dC, C.shape), want) <= tol(K)
