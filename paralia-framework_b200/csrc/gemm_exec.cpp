@@ -45,7 +45,7 @@ struct OperandDesc {
   int loc = -1;          // -1 host, >=0 GPU
   bool trans = false;    // stored transposed w.r.t. its role in the GEMM
   int64_t rows = 0, cols = 0;  // stored extent
-  bool registered_here = false;
+  HostPin pin;   // page-lock taken by this call, if any
 };
 
 // Where one tile of an operand can be read on one GPU.
@@ -138,41 +138,10 @@ int norm_trans(char t, bool* out) {
 
 // Resolve where an operand lives and make host memory DMA-able.
 int resolve_operand(OperandDesc* op, int loc_in, size_t bytes, int ngpu, double* pin_ms) {
-  bool pinned = false;
-  const int actual = pointer_location(op->ptr, &pinned);
-  int loc = loc_in;
-  if (loc == PARALIA_LOC_AUTO) loc = actual;
-  if (loc < -1 || loc >= ngpu)
-    return fail(PARALIA_ERR_INVALID_ARG, "location id %d is neither -1 nor a GPU of this box", loc);
-  if (loc >= 0 && actual != loc)
-    return fail(PARALIA_ERR_INVALID_ARG, "operand declared on GPU %d but the pointer lives on %d",
-                loc, actual);
-  if (loc == -1 && actual >= 0)
-    return fail(PARALIA_ERR_INVALID_ARG, "operand declared on the host but the pointer is on GPU %d",
-                actual);
-  op->loc = loc;
-  if (loc == -1 && !pinned && bytes > 0) {
-    // The reference pins host operands in place for the call (Decom2D::prepareAsync,
-    // dgemm.cpp:413-416) and unpins them at teardown (dgemm.cpp:669-678).
-    const double t0 = wall_ms();
-    cudaError_t e = cudaHostRegister(const_cast<void*>(op->ptr), bytes, cudaHostRegisterPortable);
-    if (e != cudaSuccess) {
-      cudaGetLastError();
-      return fail(PARALIA_ERR_CUDA, "cannot page-lock a host operand of %zu bytes: %s", bytes,
-                  cudaGetErrorString(e));
-    }
-    op->registered_here = true;
-    if (pin_ms) *pin_ms += wall_ms() - t0;
-  }
-  return PARALIA_OK;
+  return resolve_operand_location(op->ptr, loc_in, bytes, ngpu, &op->loc, &op->pin, pin_ms);
 }
 
-void unpin(OperandDesc* op) {
-  if (op->registered_here) {
-    cudaHostUnregister(const_cast<void*>(op->ptr));
-    op->registered_here = false;
-  }
-}
+void unpin(OperandDesc* op) { op->pin.release(); }
 
 template <typename T>
 struct TileGeom {

@@ -22,40 +22,15 @@ struct VecDesc {
   const double* ptr = nullptr;
   int64_t inc = 1;
   int loc = -1;
-  bool registered_here = false;
+  HostPin pin;   // page-lock taken by this call, if any
 };
 
 int resolve_vec(VecDesc* v, int loc_in, int64_t n, int ngpu, double* pin_ms) {
-  bool pinned = false;
-  const int actual = pointer_location(v->ptr, &pinned);
-  int loc = loc_in == PARALIA_LOC_AUTO ? actual : loc_in;
-  if (loc < -1 || loc >= ngpu)
-    return fail(PARALIA_ERR_INVALID_ARG, "location id %d is neither -1 nor a GPU of this box", loc);
-  if ((loc >= 0) != (actual >= 0) || (loc >= 0 && loc != actual))
-    return fail(PARALIA_ERR_INVALID_ARG, "vector declared at location %d but the pointer lives at %d",
-                loc, actual);
-  v->loc = loc;
-  if (loc == -1 && !pinned && n > 0) {
-    const double t0 = wall_ms();
-    const size_t bytes = (size_t)(1 + (n - 1) * std::llabs(v->inc)) * sizeof(double);
-    cudaError_t e = cudaHostRegister(const_cast<double*>(v->ptr), bytes, cudaHostRegisterPortable);
-    if (e != cudaSuccess) {
-      cudaGetLastError();
-      return fail(PARALIA_ERR_CUDA, "cannot page-lock a host vector of %zu bytes: %s", bytes,
-                  cudaGetErrorString(e));
-    }
-    v->registered_here = true;
-    if (pin_ms) *pin_ms += wall_ms() - t0;
-  }
-  return PARALIA_OK;
+  const size_t bytes = n > 0 ? (size_t)(1 + (n - 1) * std::llabs(v->inc)) * sizeof(double) : 0;
+  return resolve_operand_location(v->ptr, loc_in, bytes, ngpu, &v->loc, &v->pin, pin_ms);
 }
 
-void unpin(VecDesc* v) {
-  if (v->registered_here) {
-    cudaHostUnregister(const_cast<double*>(v->ptr));
-    v->registered_here = false;
-  }
-}
+void unpin(VecDesc* v) { v->pin.release(); }
 
 constexpr int RING = 4;  // cache blocks per vector and GPU
 

@@ -21,42 +21,6 @@ namespace {
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 inline size_t align_up(size_t a, size_t b) { return (a + b - 1) / b * b; }
 
-struct HostPin {
-  const void* ptr = nullptr;
-  bool registered = false;
-  void release() {
-    if (registered) cudaHostUnregister(const_cast<void*>(ptr));
-    registered = false;
-  }
-};
-
-// Resolve a location id against the pointer and page-lock pageable host memory.
-int resolve(const void* ptr, int loc_in, size_t bytes, int ngpu, int* loc_out, HostPin* pin,
-            double* pin_ms) {
-  bool pinned = false;
-  const int actual = pointer_location(ptr, &pinned);
-  const int loc = loc_in == PARALIA_LOC_AUTO ? actual : loc_in;
-  if (loc < -1 || loc >= ngpu)
-    return fail(PARALIA_ERR_INVALID_ARG, "location id %d is neither -1 nor a GPU of this box", loc);
-  if ((loc >= 0) != (actual >= 0) || (loc >= 0 && loc != actual))
-    return fail(PARALIA_ERR_INVALID_ARG, "operand declared at location %d but the pointer lives at %d",
-                loc, actual);
-  *loc_out = loc;
-  if (loc == -1 && !pinned && bytes > 0) {
-    const double t0 = wall_ms();
-    cudaError_t e = cudaHostRegister(const_cast<void*>(ptr), bytes, cudaHostRegisterPortable);
-    if (e != cudaSuccess) {
-      cudaGetLastError();
-      return fail(PARALIA_ERR_CUDA, "cannot page-lock a host operand of %zu bytes: %s", bytes,
-                  cudaGetErrorString(e));
-    }
-    pin->ptr = ptr;
-    pin->registered = true;
-    if (pin_ms) *pin_ms += wall_ms() - t0;
-  }
-  return PARALIA_OK;
-}
-
 struct GvUnit {
   int dev;
   int64_t o_lo, o_hi;          // run of the output vector
@@ -103,9 +67,9 @@ int exec_dgemv(char TransA, int64_t M, int64_t N, double alpha, const double* A,
   HostPin pins[3];
   double pin_ms = 0.0;
   int lA = -1, lx = -1, ly = -1;
-  int rc = resolve(A, locA, (size_t)ldA * N * 8, ngpu, &lA, &pins[0], &pin_ms);
-  if (rc == PARALIA_OK) rc = resolve(x, locx, (size_t)(1 + (in_len - 1) * incx) * 8, ngpu, &lx, &pins[1], &pin_ms);
-  if (rc == PARALIA_OK) rc = resolve(y, locy, (size_t)(1 + (out_len - 1) * incy) * 8, ngpu, &ly, &pins[2], &pin_ms);
+  int rc = resolve_operand_location(A, locA, (size_t)ldA * N * 8, ngpu, &lA, &pins[0], &pin_ms);
+  if (rc == PARALIA_OK) rc = resolve_operand_location(x, locx, (size_t)(1 + (in_len - 1) * incx) * 8, ngpu, &lx, &pins[1], &pin_ms);
+  if (rc == PARALIA_OK) rc = resolve_operand_location(y, locy, (size_t)(1 + (out_len - 1) * incy) * 8, ngpu, &ly, &pins[2], &pin_ms);
   const bool keep_pinned = ctl && (ctl->flags & PARALIA_FLAG_KEEP_PINNED);
   auto cleanup = [&]() { if (!keep_pinned) for (auto& p : pins) p.release(); };
   if (rc != PARALIA_OK) { cleanup(); return rc; }

@@ -58,6 +58,40 @@ int Runtime::init() {
   return PARALIA_OK;
 }
 
+void HostPin::release() {
+  if (registered) cudaHostUnregister(const_cast<void*>(ptr));
+  registered = false;
+}
+
+int resolve_operand_location(const void* ptr, int loc_in, size_t bytes, int ngpu, int* loc_out,
+                             HostPin* pin, double* pin_ms) {
+  bool pinned = false;
+  const int actual = pointer_location(ptr, &pinned);
+  const int loc = loc_in == PARALIA_LOC_AUTO ? actual : loc_in;
+  if (loc < -1 || loc >= ngpu)
+    return fail(PARALIA_ERR_INVALID_ARG, "location id %d is neither -1 nor a GPU of this box", loc);
+  if (loc >= 0 && actual != loc)
+    return fail(PARALIA_ERR_INVALID_ARG, "operand declared on GPU %d but the pointer lives on %d",
+                loc, actual);
+  if (loc == -1 && actual >= 0)
+    return fail(PARALIA_ERR_INVALID_ARG, "operand declared on the host but the pointer is on GPU %d",
+                actual);
+  *loc_out = loc;
+  if (loc == -1 && !pinned && bytes > 0) {
+    const double t0 = wall_ms();
+    cudaError_t e = cudaHostRegister(const_cast<void*>(ptr), bytes, cudaHostRegisterPortable);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return fail(PARALIA_ERR_CUDA, "cannot page-lock a host operand of %zu bytes: %s", bytes,
+                  cudaGetErrorString(e));
+    }
+    pin->ptr = ptr;
+    pin->registered = true;
+    if (pin_ms) *pin_ms += wall_ms() - t0;
+  }
+  return PARALIA_OK;
+}
+
 int Runtime::order_after_caller(const std::vector<int>& devs, const std::vector<int>& units) {
   std::vector<int> marked;
   for (int d : devs) {

@@ -121,6 +121,21 @@ struct DeviceGuard {
 // tells which), 0..G-1 for device memory. Reference: CoCoGetPtrLoc.
 int pointer_location(const void* p, bool* pinned);
 
+// The page-lock a call took on a pageable host operand (the reference pins host operands
+// in place for the call, Decom2D::prepareAsync at dgemm.cpp:413-416, and unpins them at
+// teardown, dgemm.cpp:669-678).
+struct HostPin {
+  const void* ptr = nullptr;
+  bool registered = false;
+  void release();
+};
+
+// Check the location a caller declared for an operand (PARALIA_LOC_AUTO = ask the driver)
+// against where the pointer really lives, and page-lock `bytes` of it if it is pageable
+// host memory. *loc_out receives -1 (host) or the GPU id.
+int resolve_operand_location(const void* ptr, int loc_in, size_t bytes, int ngpu, int* loc_out,
+                             HostPin* pin, double* pin_ms);
+
 // 3-D tiled TMA descriptor over {d0 (contiguous), d1, d2} elements of `esz` bytes with
 // 128-byte swizzle and zero fill outside the tensor.
 int make_tensor_map(CUtensorMap* map, const void* base, int esz, uint64_t d0, uint64_t d1,
