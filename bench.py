@@ -326,8 +326,10 @@ def main():
         # flops_total / launches. Launches on the library's execution streams overlap, so
         # the per-launch duration is the device time of the timed region (CUDA events on
         # the library's own streams) divided by the launches in it.
+        # GPUs the launches are spread over: the ranks, or the units one process drives
+        nu = max(int(ctl.active_unit_num), 1) if args.inproc else world
         per_launch_flop = flops_total * args.steps / max(launches, 1)
-        per_launch_s = dev_ms_step * 1e-3 * args.steps / max(launches / world, 1)
+        per_launch_s = dev_ms_step * 1e-3 * args.steps / max(launches / nu, 1)
         achieved = per_launch_flop / per_launch_s / 1e12
         cpu = None
         if not args.no_cpu and world == 1:
@@ -338,7 +340,7 @@ def main():
                               f"{ts:.1f} s, {cores} threads")}
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s",
-            "n_gpus": (len(list(ctl.active_unit_id_list[:ctl.active_unit_num])) if args.inproc else world),
+            "n_gpus": nu,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f64", "data": "synthetic",
@@ -356,14 +358,14 @@ def main():
             "roofline": {
                 "bound": "tensor", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
                 "frac": achieved / peak_tf if peak_tf else None,
-                # DRAM bytes per launch: algorithmic bytes of an average launch (its share of
-                # the A row panel and B column panel of its C tile, plus C read and written)
+                # DRAM bytes per launch: algorithmic bytes of an average launch = (one A and one
+                # B tile read per (mi, ni, ki) step, plus one C tile read and written per launch,
+                # summed over the step's launches on all GPUs) / launches per step,
                 # times the 1.30 ratio of measured to algorithmic bytes from the ncu capture
                 # of the same kernel on a small case
-                "traffic": 1.30 * 8.0 * (2.0 * Mloc * Nloc * K / max(rep.T, 1) + 2.0 * Mloc * Nloc
-                                         * max(launches // max(args.steps, 1) // world, 1)
-                                         / max((Mloc // max(rep.T, 1)) * (Nloc // max(rep.T, 1)), 1))
-                           / max(launches // max(args.steps, 1) // world, 1),
+                "traffic": 1.30 * 8.0 * (2.0 * float(n) ** 3 / max(rep.T, 1)
+                                         + 2.0 * float(rep.T) ** 2 * max(launches // max(args.steps, 1), 1))
+                           / max(launches // max(args.steps, 1), 1),
                 "traffic_source": "algorithmic bytes x 1.30 (ncu dram__bytes of this kernel on a "
                                   "4096^3 case, profiles/dgemm_tile_kernel_n4096_ncu_full.md)",
                 "peak_source": "FP64 DMMA register-loop microbenchmark run in this process "
