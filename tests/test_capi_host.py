@@ -187,3 +187,36 @@ def test_packaged_database_loads_and_fills_unmeasured_links(pl):
     # measured: 2.0 s on one GPU, 0.25 s of compute on eight
     assert 1.8 < t1 < 2.3
     assert 0.22 < t8 < 0.33
+
+
+def test_sweep_matrix_is_the_reference_evaluation_matrix(pl):
+    # Benchmarking/Full_performance_evaluation.in: 10 placement scenarios; squares
+    # 2048..22528 step 1024; thin K = MN/{2,8,32} for MN 8192..32768 step 4096; fat K
+    # 12288..36864 step 4096 with MN = K/{2,8,32}
+    import importlib
+    sweep = importlib.import_module("paralia_framework_b200.sweep")
+    assert len(sweep.SCENARIOS) == 10
+    assert sweep.SCENARIOS["Full_offload"] == (-1, -1, -1)
+    assert sweep.SCENARIOS["Partial_offload_mixed"] == (-1, 0, 5)
+    assert sweep.SCENARIOS["Device_only_offload_mixed4"] == (1, 6, 7)
+    sq = sweep.shapes("square", False)
+    assert len(sq) == 21 and sq[0] == (2048,) * 3 and sq[-1] == (22528,) * 3
+    thin = sweep.shapes("thin", False)
+    assert len(thin) == 21 and (8192, 8192, 4096) in thin and (32768, 32768, 1024) in thin
+    fat = sweep.shapes("fat", False)
+    assert len(fat) == 21 and (6144, 6144, 12288) in fat and (1152, 1152, 36864) in fat
+    assert all(len(sweep.shapes(f, True)) <= 3 for f in ("square", "thin", "fat"))
+    # ids of an 8-GPU box folded onto a smaller one; the host stays the host
+    assert [sweep.fold(v, 2) for v in (-1, 0, 5, 6)] == [-1, 0, 1, 0]
+    assert (sweep.ALPHA, sweep.BETA) == (1.2345, 1.1154)
+
+
+def test_comparator_binds_the_vendor_symbols():
+    # the yardstick module only loads the toolkit's cuBLAS; nothing is computed without a GPU
+    import importlib
+    comparators = importlib.import_module("paralia_framework_b200.comparators")
+    lib = comparators.cublas()
+    for name in ("cublasXtCreate", "cublasXtDeviceSelect", "cublasXtSetBlockDim", "cublasXtSetCpuRatio",
+                 "cublasXtSetPinningMemMode", "cublasXtDgemm", "cublasXtSgemm", "cublasXtDestroy",
+                 "cublasDgemm_v2", "cublasSgemm_v2"):
+        assert hasattr(lib, name), name
