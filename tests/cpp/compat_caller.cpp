@@ -138,7 +138,7 @@ int main() {
     r = PARALiADaxpy(n, -0.5, x.data(), 1, y.data(), 1);
     report("PARALiADaxpy", rel_err(y, want), 0.0, r);
   }
-  for (short d = -1; d < 16; ++d) PARALiADevCacheFree(d);   // as the reference's runner does
+  for (short d = 0; d < (short)PARALiA_device_count(); ++d) PARALiADevCacheFree(d);   // as the reference's runner does
   std::printf("%s\n", failures ? "MISMATCH" : "ALL OK");
   return failures ? 1 : 0;
 }

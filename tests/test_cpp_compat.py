@@ -41,4 +41,4 @@ def test_reference_style_caller_runs(pl, tmp_path):
     res = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300, env=env)
     assert res.returncode == 0, res.stdout + res.stderr
     assert "ALL OK" in res.stdout and "FAILED" not in res.stdout
-    assert res.stdout.count(" ok") == 8
+    assert res.stdout.count(" ok\n") == 7     # seven report lines
