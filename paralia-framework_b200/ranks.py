@@ -53,14 +53,21 @@ def vector_chunk(rank: int, world: int, N: int, quantum: int = 1) -> tuple[int, 
 
 
 def allreduce_sum(value: float, device=None) -> float:
-    """Sum of one double over all ranks (DDOT's cross-GPU reduction). Rank partials are
-    added by the backend (NCCL on GPUs, gloo on CPUs); with torch.distributed not
+    """Sum of one double over all ranks (DDOT's cross-GPU reduction; the reference adds the
+    per-tile partials on the host in tile order, ddot.cpp:431). The rank partials are
+    gathered (NCCL on GPUs, gloo on CPUs) and added in rank order on every rank, so all
+    ranks return the same bits and a rerun reproduces them; a reducing collective would
+    leave the order of the additions to the backend. With torch.distributed not
     initialised the value is returned unchanged."""
     import torch
     import torch.distributed as dist
 
     if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
         return float(value)
-    t = torch.tensor([value], dtype=torch.float64, device=device)
-    dist.all_reduce(t, op=dist.ReduceOp.SUM)
-    return float(t.item())
+    mine = torch.tensor([value], dtype=torch.float64, device=device)
+    parts = [torch.empty_like(mine) for _ in range(dist.get_world_size())]
+    dist.all_gather(parts, mine)
+    total = 0.0
+    for p in parts:            # rank order
+        total += float(p.item())
+    return total

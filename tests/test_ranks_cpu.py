@@ -43,6 +43,7 @@ def _worker(rank, world, port, M, N, K, nvec, out_dir):
     lo, hi = ranks.vector_chunk(rank, world, nvec, quantum=64)
     part, _ = orc.ddot_tiled(hi - lo, x[lo:], 1, y[lo:], 1, 128, 0.0)
     total = ranks.allreduce_sum(part)
+    np.save(os.path.join(out_dir, f"dot_rank{rank}.npy"), np.array([part, total]))
     cover = torch.zeros(nvec, dtype=torch.int32)
     cover[lo:hi] += 1
     dist.all_reduce(cover)
@@ -71,6 +72,12 @@ def test_rank_partition_reassembles_whole_problem(orc, tmp_path, world):
     dot, mag = orc.ddot_tiled(nvec, x, 1, y, 1, 128, 0.0)
     assert abs(np.load(tmp_path / "dot.npy")[0] - dot) <= nvec * 2.0 ** -52 * mag
     assert (np.load(tmp_path / "cover.npy") == 1).all()   # every element owned exactly once
+    # the rank partials are added in rank order on every rank: same bits everywhere
+    per_rank = [np.load(tmp_path / f"dot_rank{r}.npy") for r in range(world)]
+    ordered = 0.0
+    for part, _ in per_rank:
+        ordered += float(part)
+    assert all(float(total) == ordered for _, total in per_rank)
 
 
 def test_gemm_block_grid_matches_library(pl):
