@@ -319,7 +319,14 @@ def main(argv=None) -> dict:
     a = ap.parse_args(argv)
     r = a.rest
     pl = _pkg()
-    pl.init()
+    try:
+        pl.init()
+    except pl.ParaliaError:
+        # the predictor needs no GPU when the unit list is given: the model runs on the host
+        if not (a.routine.endswith("_predict") and a.active_unit_num > 0):
+            raise
+        if (pl.DEFAULT_DB / "Processed").is_dir():
+            pl.load_database(str(pl.DEFAULT_DB))
     a.comparator = a.routine.startswith("cublasxt_")
     if a.comparator:
         a.routine = a.routine[len("cublasxt_"):]

@@ -220,3 +220,21 @@ def test_comparator_binds_the_vendor_symbols():
                  "cublasXtSetPinningMemMode", "cublasXtDgemm", "cublasXtSgemm", "cublasXtDestroy",
                  "cublasDgemm_v2", "cublasSgemm_v2"):
         assert hasattr(lib, name), name
+
+
+def test_predictor_mode_needs_no_gpu_with_a_unit_list(pl, capsys):
+    # the reference's dgemm_predictor: autotune only; with the units given the model runs on
+    # the host alone (shipped B200 tables)
+    import importlib
+    runner = importlib.import_module("paralia_framework_b200.runner")
+    out = runner.main(["dgemm_predict", "8", "11111111", "-1", "-1", "N", "N", "1", "1",
+                       "32768", "32768", "32768", "-1", "-1", "-1", "-1"])
+    capsys.readouterr()
+    assert out["T"] == 2048 and out["grid"] == [2, 4] and out["units"] == list(range(8))
+    assert out["subkernels"] == 16 ** 3
+    # host-resident 32768^3 on 8 B200: the model says compute-bound, 0.25-0.30 s
+    assert 0.25 < out["pred_t"] < 0.30
+    one = runner.main(["dgemm_predict", "1", "1", "-1", "-1", "N", "N", "1", "1",
+                       "32768", "32768", "32768", "-1", "-1", "-1", "-1"])
+    capsys.readouterr()
+    assert one["T"] == 4096 and 1.9 < one["pred_t"] < 2.2
