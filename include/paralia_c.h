@@ -211,6 +211,17 @@ int PARALiA_tile_ddot(int dev, void* stream, int64_t N,
                       const double* x, int64_t incx, const double* y, int64_t incy,
                       double* partials, double* result_dev);
 
+/* Per-tile FP64 matrix-vector product y <- alpha*op(A)*x + beta*y on the caller's stream:
+ * the compute call behind the reference's DGEMV subkernels (backend_run_operation with
+ * "Dgemv", Library_scheduler/src/Subkernel.cpp:168,228, set up in
+ * Library_scheduler/src/Functions/dgemv.cpp). A is M x N column-major on GPU `dev`.
+ * `scratch` is device memory of PARALiA_tile_dgemv_scratch_bytes(TransA, M, N) bytes
+ * (op = N keeps partial vectors there; op = T needs none and accepts NULL). */
+int64_t PARALiA_tile_dgemv_scratch_bytes(char TransA, int64_t M, int64_t N);
+int PARALiA_tile_dgemv(int dev, void* stream, char TransA, int64_t M, int64_t N, double alpha,
+                       const double* A, int64_t ldA, const double* x, int64_t incx,
+                       double beta, double* y, int64_t incy, double* scratch);
+
 /* Dot product that allocates nothing. It has no counterpart in the reference.
  * For callers that cannot call cudaMalloc where they need the result (inside a
  * latency-critical loop where an allocation would stall the device, inside a host

@@ -138,6 +138,9 @@ SIGNATURES = {
     "PARALiA_tile_daxpy": (C.c_int, [C.c_int, _vp, _i64, _dbl, _vp, _i64, _vp, _i64]),
     "PARALiA_tile_ddot_scratch_bytes": (_i64, [_i64]),
     "PARALiA_tile_ddot": (C.c_int, [C.c_int, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp]),
+    "PARALiA_tile_dgemv_scratch_bytes": (_i64, [_chr, _i64, _i64]),
+    "PARALiA_tile_dgemv": (C.c_int, [C.c_int, _vp, _chr, _i64, _i64, _dbl, _vp, _i64, _vp, _i64,
+                                     _dbl, _vp, _i64, _vp]),
     "PARALiA_tile_ddot_noalloc_max_n": (_i64, []),
     "PARALiA_tile_ddot_noalloc": (C.c_int, [C.c_int, _vp, _i64, _vp, _i64, _vp, _i64, _vp]),
     "PARALiA_malloc": (C.c_int, [C.POINTER(_vp), _i64, C.c_int]),
@@ -346,6 +349,17 @@ def tile_ddot_scratch_bytes(N: int) -> int:
 def tile_ddot(dev, N, x, incx, y, incy, partials, result_dev, stream: int = 0) -> None:
     _check(lib().PARALiA_tile_ddot(dev, stream, N, _ptr(x), incx, _ptr(y), incy, _ptr(partials),
                                    _ptr(result_dev)))
+
+
+def tile_dgemv_scratch_bytes(TransA, M, N) -> int:
+    return int(lib().PARALiA_tile_dgemv_scratch_bytes(_c(TransA), M, N))
+
+
+def tile_dgemv(dev, TransA, M, N, alpha, A, ldA, x, incx, beta, y, incy, scratch=None,
+               stream: int = 0) -> None:
+    """Per-tile DGEMV on the caller's stream (reference: the "Dgemv" backend operation)."""
+    _check(lib().PARALiA_tile_dgemv(dev, stream, _c(TransA), M, N, alpha, _ptr(A), ldA, _ptr(x), incx,
+                                    beta, _ptr(y), incy, _ptr(scratch)))
 
 
 def tile_ddot_noalloc_max_n() -> int:

@@ -11,6 +11,7 @@
 #include "exec.hpp"
 #include "group.hpp"
 #include "level1.cuh"
+#include "level2.cuh"
 #include "paralia_rng.h"
 #include "runtime.hpp"
 #include "sgemm_tile.cuh"
@@ -186,6 +187,34 @@ int PARALiA_tile_ddot(int dev, void* stream, int64_t N, const double* x, int64_t
   PL_TRY(setup_device(dev));
   PL_CUDA(launch_ddot(N, x, incx, y, incy, partials, result_dev, static_cast<cudaStream_t>(stream),
                       nullptr));
+  return PARALIA_OK;
+}
+
+int64_t PARALiA_tile_dgemv_scratch_bytes(char TransA, int64_t M, int64_t N) {
+  if (!valid_t(TransA) || M <= 0 || N <= 0 || M > INT32_MAX || N > INT32_MAX) return 0;
+  if (norm_t(TransA)) return 0;
+  return (int64_t)gemv_n_slices((int)M, (int)N) * M * (int64_t)sizeof(double);
+}
+
+int PARALiA_tile_dgemv(int dev, void* stream, char TransA, int64_t M, int64_t N, double alpha,
+                       const double* A, int64_t ldA, const double* x, int64_t incx, double beta,
+                       double* y, int64_t incy, double* scratch) {
+  if (!valid_t(TransA)) return fail(PARALIA_ERR_INVALID_ARG, "transpose flag is not N or T");
+  if (M < 0 || N < 0 || M > INT32_MAX || N > INT32_MAX)
+    return fail(PARALIA_ERR_INVALID_ARG, "dimension out of range");
+  if (incx <= 0 || incy <= 0) return fail(PARALIA_ERR_UNSUPPORTED, "non-positive increments are not supported");
+  if (ldA < std::max<int64_t>(1, M))
+    return fail(PARALIA_ERR_INVALID_ARG, "leading dimension smaller than the row count");
+  const bool trans = norm_t(TransA) != 0;
+  const int64_t out_len = trans ? N : M, in_len = trans ? M : N;
+  if (out_len == 0) return PARALIA_OK;
+  if (in_len == 0) return fail(PARALIA_ERR_UNSUPPORTED, "empty product: scale y with PARALiA_tile_daxpy");
+  if (!A || !x || !y) return fail(PARALIA_ERR_INVALID_ARG, "NULL operand");
+  if (!trans && !scratch) return fail(PARALIA_ERR_INVALID_ARG, "op = N needs scratch");
+  DeviceGuard guard;
+  PL_TRY(setup_device(dev));
+  PL_CUDA(launch_dgemv_tile(trans, (int)M, (int)N, alpha, A, ldA, x, incx, beta, y, incy, scratch,
+                            static_cast<cudaStream_t>(stream), nullptr));
   return PARALIA_OK;
 }
 

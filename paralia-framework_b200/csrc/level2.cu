@@ -22,7 +22,7 @@ constexpr int GV_XCHUNK = 512;   // x values staged in shared memory at a time
 // partial[slice][m] = sum over the slice's columns of A[m, n] * x[n]
 __global__ void __launch_bounds__(GV_THREADS)
 dgemv_n_partial_kernel(int rows, int cols, const double* __restrict__ A, int64_t lda,
-                       const double* __restrict__ x, int cols_per_slice,
+                       const double* __restrict__ x, int64_t incx, int cols_per_slice,
                        double* __restrict__ partial, int vec_ok) {
   __shared__ double xs[GV_XCHUNK];
   const int m = (blockIdx.x * GV_THREADS + threadIdx.x) * 2;
@@ -32,7 +32,7 @@ dgemv_n_partial_kernel(int rows, int cols, const double* __restrict__ A, int64_t
   for (int n0 = n_begin; n0 < n_end; n0 += GV_XCHUNK) {
     const int cnt = min(GV_XCHUNK, n_end - n0);
     __syncthreads();
-    for (int i = threadIdx.x; i < cnt; i += GV_THREADS) xs[i] = x[n0 + i];
+    for (int i = threadIdx.x; i < cnt; i += GV_THREADS) xs[i] = x[(int64_t)(n0 + i) * incx];
     __syncthreads();
     if (m + 1 < rows && vec_ok) {
       const double* col = A + m + (int64_t)n0 * lda;
@@ -72,8 +72,8 @@ dgemv_n_combine_kernel(int rows, int slices, const double* __restrict__ partial,
 // y[n] = alpha * dot(A[:, n], x) + beta * y[n], one warp per column
 __global__ void __launch_bounds__(GV_THREADS)
 dgemv_t_kernel(int rows, int cols, const double* __restrict__ A, int64_t lda,
-               const double* __restrict__ x, double alpha, double beta, double* __restrict__ y,
-               int64_t incy, int vec_ok) {
+               const double* __restrict__ x, int64_t incx, double alpha, double beta,
+               double* __restrict__ y, int64_t incy, int vec_ok) {
   const int lane = threadIdx.x & 31;
   const int n = blockIdx.x * (GV_THREADS / 32) + (threadIdx.x >> 5);
   if (n >= cols) return;
@@ -99,7 +99,7 @@ dgemv_t_kernel(int rows, int cols, const double* __restrict__ A, int64_t lda,
     }
     if ((rows & 1) && lane == 0) acc[1] = fma(col[rows - 1], x[rows - 1], acc[1]);
   } else {
-    for (int i = lane; i < rows; i += 32) acc[0] = fma(col[i], x[i], acc[0]);
+    for (int i = lane; i < rows; i += 32) acc[0] = fma(col[i], x[(int64_t)i * incx], acc[0]);
   }
   double s = (acc[0] + acc[1]) + (acc[2] + acc[3]);
 #pragma unroll
@@ -124,24 +124,24 @@ int gemv_n_slices(int rows, int cols) {
 }
 
 cudaError_t launch_dgemv_tile(bool trans, int rows, int cols, double alpha, const double* A,
-                              int64_t lda, const double* x, double beta, double* y, int64_t incy,
-                              double* partial, cudaStream_t stream, int* launches) {
+                              int64_t lda, const double* x, int64_t incx, double beta, double* y,
+                              int64_t incy, double* partial, cudaStream_t stream, int* launches) {
   if (rows <= 0 || cols <= 0) return cudaSuccess;
   const bool a_ok = (reinterpret_cast<uintptr_t>(A) & 15) == 0 && (lda & 1) == 0;
   if (!trans) {
     const int slices = gemv_n_slices(rows, cols);
     const int cps = (cols + slices - 1) / slices;
     dim3 grid((rows + GV_THREADS * 2 - 1) / (GV_THREADS * 2), slices);
-    dgemv_n_partial_kernel<<<grid, GV_THREADS, 0, stream>>>(rows, cols, A, lda, x, cps, partial,
+    dgemv_n_partial_kernel<<<grid, GV_THREADS, 0, stream>>>(rows, cols, A, lda, x, incx, cps, partial,
                                                             a_ok ? 1 : 0);
     dgemv_n_combine_kernel<<<(rows + GV_THREADS - 1) / GV_THREADS, GV_THREADS, 0, stream>>>(
         rows, slices, partial, alpha, beta, y, incy);
     if (launches) *launches += 2;
   } else {
-    const bool x_ok = (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+    const bool x_ok = (reinterpret_cast<uintptr_t>(x) & 15) == 0 && incx == 1;
     const int warps = GV_THREADS / 32;
     dgemv_t_kernel<<<(cols + warps - 1) / warps, GV_THREADS, 0, stream>>>(
-        rows, cols, A, lda, x, alpha, beta, y, incy, (a_ok && x_ok) ? 1 : 0);
+        rows, cols, A, lda, x, incx, alpha, beta, y, incy, (a_ok && x_ok) ? 1 : 0);
     if (launches) *launches += 1;
   }
   return cudaGetLastError();

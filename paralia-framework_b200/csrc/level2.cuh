@@ -10,10 +10,11 @@ namespace paralia {
 int gemv_n_slices(int rows, int cols);
 
 // y <- alpha*op(A)*x + beta*y for one column-major rows x cols tile on the current device.
-// x is contiguous (rows elements if trans, else cols); y has rows (op = N) or cols (op = T)
-// elements with increment incy. `partial` (op = N only) holds gemv_n_slices()*rows doubles.
+// x has rows (op = T) or cols (op = N) elements with increment incx; y has rows (op = N) or
+// cols (op = T) elements with increment incy. `partial` (op = N only) holds
+// gemv_n_slices()*rows doubles.
 cudaError_t launch_dgemv_tile(bool trans, int rows, int cols, double alpha, const double* A,
-                              int64_t lda, const double* x, double beta, double* y, int64_t incy,
-                              double* partial, cudaStream_t stream, int* launches);
+                              int64_t lda, const double* x, int64_t incx, double beta, double* y,
+                              int64_t incy, double* partial, cudaStream_t stream, int* launches);
 
 }  // namespace paralia

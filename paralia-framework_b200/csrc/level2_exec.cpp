@@ -224,11 +224,11 @@ int exec_dgemv(char TransA, int64_t M, int64_t N, double alpha, const double* A,
       int launches = 0;
       if (!trans) {
         // this tile adds its columns' contribution to the whole run of y
-        PL_CUDA(launch_dgemv_tile(false, (int)rows, (int)cn, alpha, a_tile, lda_tile, u.x_dev + c0,
+        PL_CUDA(launch_dgemv_tile(false, (int)rows, (int)cn, alpha, a_tile, lda_tile, u.x_dev + c0, 1,
                                   j == 0 ? beta : 1.0, u.y_dev, u.y_inc, u.partial, es, &launches));
       } else {
         // this tile finishes y[c0 .. c0+cn) of the run
-        PL_CUDA(launch_dgemv_tile(true, (int)rows, (int)cn, alpha, a_tile, lda_tile, u.x_dev, beta,
+        PL_CUDA(launch_dgemv_tile(true, (int)rows, (int)cn, alpha, a_tile, lda_tile, u.x_dev, 1, beta,
                                   u.y_dev + c0 * u.y_inc, u.y_inc, nullptr, es, &launches));
       }
       rep->kernel_launches += launches;

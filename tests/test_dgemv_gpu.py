@@ -85,3 +85,43 @@ def test_dgemv_invalid_arguments(pl, orc):
     with pytest.raises(pl.ParaliaError) as e:
         pl.dgemv("Q", 8, 8, 1.0, A, 8, x, 1, 0.0, x, 1)
     assert e.value.code == pl.ERR_INVALID_ARG
+
+
+@pytest.mark.parametrize("ta", ["N", "T"])
+@pytest.mark.parametrize("dims,pad,incx,incy", [((1024, 768), 0, 1, 1), ((289, 353), 1, 1, 1),
+                                               ((513, 1025), 3, 2, 3), ((1, 300), 0, 1, 1),
+                                               ((300, 1), 0, 3, 1)])
+def test_tile_dgemv_vs_oracle(pl, orc, ta, dims, pad, incx, incy):
+    # the per-tile entry on the caller's stream, strided x and y, odd leading dimension
+    import torch
+    M, N = dims
+    A, x, y, in_len, out_len = _case(orc, ta, M, N, pad, incx, incy)
+    want = y.copy()
+    orc.dgemv(ta, M, N, -0.75, A, M + pad, x, incx, 1.5, want, incy)
+    dA = torch.from_numpy(np.ascontiguousarray(A.T)).cuda()     # same bytes as column-major
+    dx, dy = torch.from_numpy(x).cuda(), torch.from_numpy(y.copy()).cuda()
+    nbytes = pl.tile_dgemv_scratch_bytes(ta, M, N)
+    assert (nbytes == 0) == (ta == "T")
+    scratch = torch.empty(max(nbytes // 8, 1), dtype=torch.float64, device="cuda")
+    stream = torch.cuda.current_stream()
+    pl.tile_dgemv(0, ta, M, N, -0.75, dA, M + pad, dx, incx, 1.5, dy, incy,
+                  scratch if nbytes else None, stream=stream.cuda_stream)
+    stream.synchronize()
+    got = dy.cpu().numpy()
+    assert orc.normwise_rel_err(got[::incy], want[::incy]) <= 8 * in_len * EPS64
+    if incy > 1:
+        mask = np.ones(len(y), bool); mask[::incy] = False
+        assert np.array_equal(got[mask], y[mask])
+
+
+def test_tile_dgemv_invalid_arguments(pl):
+    import torch
+    d = torch.zeros(64, dtype=torch.float64, device="cuda")
+    with pytest.raises(pl.ParaliaError):
+        pl.tile_dgemv(0, "X", 4, 4, 1.0, d, 4, d, 1, 0.0, d, 1, d)
+    with pytest.raises(pl.ParaliaError):
+        pl.tile_dgemv(0, "N", 4, 4, 1.0, d, 2, d, 1, 0.0, d, 1, d)      # ldA < M
+    with pytest.raises(pl.ParaliaError):
+        pl.tile_dgemv(0, "N", 4, 4, 1.0, d, 4, d, 1, 0.0, d, 1, None)   # op = N without scratch
+    with pytest.raises(pl.ParaliaError):
+        pl.tile_dgemv(0, "T", 4, 4, 1.0, d, 4, d, 0, 0.0, d, 1, None)   # zero increment
