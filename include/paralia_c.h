@@ -267,6 +267,19 @@ int PARALiA_tile_slowdowns(int64_t M, int64_t N, int64_t K, int64_t T, int activ
  * d1/d2 receive the device grid. */
 int PARALiA_distribute_2d(int units, int Mt, int Nt, int Kt, int32_t* sk_unit,
                           int32_t* d1, int32_t* d2);
+/* The launch plan of a tiled GEMM with `units` GPUs and tile edge T, in the order the
+ * launches are enqueued (round-robin over the units, one launch per turn): for launch i,
+ * items[5*i .. 5*i+4] = unit index, C tile row mi, C tile column ni, first k tile, end k
+ * tile. Pure host arithmetic, a function of (M, N, K, T, units, bounded_cache) alone --
+ * this is what makes the tile order, and with it the result bits, reproducible. It stands
+ * where the reference chooses the next subkernel at run time (SubkernelSelect,
+ * Library_scheduler/src/Subkernel.cpp:384-449, fire loop
+ * Library_scheduler/src/Functions/dgemm.cpp:516-544). bounded_cache != 0 gives the order
+ * used when the tile cache cannot hold a unit's working set. *count receives the number
+ * of launches; at most `capacity` of them are written (items may be NULL to ask for the
+ * count only). */
+int PARALiA_plan_gemm(int64_t M, int64_t N, int64_t K, int64_t T, int units, int bounded_cache,
+                      int32_t* items, int64_t capacity, int64_t* count, int32_t* d1, int32_t* d2);
 /* Load / replace the calibration database directory (lookup tables + link models). */
 int PARALiA_load_database(const char* dir);
 

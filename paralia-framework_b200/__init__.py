@@ -153,6 +153,8 @@ SIGNATURES = {
     "PARALiA_tile_slowdowns": (C.c_int, [_i64, _i64, _i64, _i64, C.c_int, C.POINTER(_dbl)]),
     "PARALiA_distribute_2d": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(_i32),
                                         C.POINTER(_i32), C.POINTER(_i32)]),
+    "PARALiA_plan_gemm": (C.c_int, [_i64, _i64, _i64, _i64, C.c_int, C.c_int, C.POINTER(_i32), _i64,
+                                    C.POINTER(_i64), C.POINTER(_i32), C.POINTER(_i32)]),
     "PARALiA_load_database": (C.c_int, [C.c_char_p]),
     "PARALiA_bench_dmma_peak": (C.c_int, [C.c_int, C.c_int, C.c_int, C.POINTER(_dbl)]),
     "PARALiA_bench_tile_dgemm": (C.c_int, [C.c_int, _chr, _chr, _i64, C.c_int, C.POINTER(_dbl)]),
@@ -423,6 +425,20 @@ def distribute_2d(units, Mt, Nt, Kt):
     d1, d2 = C.c_int32(), C.c_int32()
     _check(lib().PARALiA_distribute_2d(units, Mt, Nt, Kt, arr, C.byref(d1), C.byref(d2)))
     return list(arr), d1.value, d2.value
+
+
+def plan_gemm(M, N, K, T, units, bounded_cache: bool = False):
+    """Launch plan of a tiled GEMM: list of (unit, mi, ni, ki0, ki1) in enqueue order, and the
+    device grid. Reference: chosen at run time by SubkernelSelect (Subkernel.cpp:384-449)."""
+    n = C.c_int64()
+    d1, d2 = C.c_int32(), C.c_int32()
+    _check(lib().PARALiA_plan_gemm(M, N, K, T, units, int(bounded_cache), None, 0, C.byref(n),
+                                   C.byref(d1), C.byref(d2)))
+    arr = (C.c_int32 * (5 * max(n.value, 1)))()
+    _check(lib().PARALiA_plan_gemm(M, N, K, T, units, int(bounded_cache), arr, n.value, C.byref(n),
+                                   C.byref(d1), C.byref(d2)))
+    flat = list(arr)[:5 * n.value]
+    return [tuple(flat[i:i + 5]) for i in range(0, len(flat), 5)], (d1.value, d2.value)
 
 
 def load_database(path: str) -> None:

@@ -13,6 +13,7 @@
 #include "level1.cuh"
 #include "level2.cuh"
 #include "paralia_rng.h"
+#include "plan.hpp"
 #include "runtime.hpp"
 #include "sgemm_tile.cuh"
 
@@ -362,6 +363,48 @@ int PARALiA_distribute_2d(int units, int Mt, int Nt, int Kt, int32_t* sk_unit, i
   for (int i = 0; i < Mt * Nt * Kt; ++i) sk_unit[i] = -1;
   for (int u = 0; u < active; ++u)
     for (int sk : lists[u]) sk_unit[sk] = u;
+  if (d1) *d1 = g1;
+  if (d2) *d2 = g2;
+  return PARALIA_OK;
+}
+
+int PARALiA_plan_gemm(int64_t M, int64_t N, int64_t K, int64_t T, int units, int bounded_cache,
+                      int32_t* items, int64_t capacity, int64_t* count, int32_t* d1, int32_t* d2) {
+  if (M <= 0 || N <= 0 || K < 0 || T <= 0 || units <= 0 || !count || capacity < 0)
+    return fail(PARALIA_ERR_INVALID_ARG, "bad plan_gemm arguments");
+  const int64_t Mt = (M + T - 1) / T, Nt = (N + T - 1) / T, Kt = K > 0 ? (K + T - 1) / T : 0;
+  if (Mt * Nt * std::max<int64_t>(Kt, 1) > INT32_MAX)
+    return fail(PARALIA_ERR_INVALID_ARG, "too many subkernels");
+  const int kt_for_ids = (int)std::max<int64_t>(Kt, 1);
+  std::vector<std::vector<int>> lists, ctiles;
+  std::vector<int> owner;
+  int g1 = 1, g2 = 1;
+  const int active = distribute_subkernels_2d(units, (int)Mt, (int)Nt, kt_for_ids, &lists, &g1, &g2);
+  if (active <= 0) return fail(PARALIA_ERR_INVALID_ARG, "distribution failed");
+  lists.resize(active);
+  if (!plan_unit_ctiles(lists, kt_for_ids, (int)(Mt * Nt), &ctiles, &owner))
+    return fail(PARALIA_ERR_UNSUPPORTED, "distribution split one C tile across units");
+  std::vector<std::vector<LaunchItem>> per_unit(active);
+  for (int u = 0; u < active; ++u)
+    plan_launch_order((int)ctiles[u].size(), (int)Kt, bounded_cache != 0, DG_MAX_PARTS, &per_unit[u]);
+  // the executor walks the units round-robin, one launch per turn
+  int64_t n = 0;
+  std::vector<size_t> cursor(active, 0);
+  for (bool left = true; left;) {
+    left = false;
+    for (int u = 0; u < active; ++u) {
+      if (cursor[u] >= per_unit[u].size()) continue;
+      const LaunchItem it = per_unit[u][cursor[u]++];
+      if (items && n < capacity) {
+        const int ct = ctiles[u][it.order_idx];
+        int32_t* o = items + 5 * n;
+        o[0] = u; o[1] = (int32_t)(ct / Nt); o[2] = (int32_t)(ct % Nt); o[3] = it.ki0; o[4] = it.ki1;
+      }
+      ++n;
+      if (cursor[u] < per_unit[u].size()) left = true;
+    }
+  }
+  *count = n;
   if (d1) *d1 = g1;
   if (d2) *d2 = g2;
   return PARALIA_OK;

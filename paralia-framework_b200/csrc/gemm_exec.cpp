@@ -25,6 +25,7 @@
 
 #include "autotune.hpp"
 #include "dgemm_tile.cuh"
+#include "plan.hpp"
 #include "runtime.hpp"
 #include "sgemm_tile.cuh"
 #include "exec.hpp"
@@ -78,7 +79,7 @@ struct UnitState {
   CUtensorMap map_a_native, map_b_native; // user matrices on this GPU
   bool a_native_ok = false, b_native_ok = false, c_native = false;
   // Launches of this unit in enqueue order: (index into ctiles, first k tile, end k tile).
-  struct Item { int order_idx, ki0, ki1; };
+  using Item = LaunchItem;
   std::vector<Item> items;
   size_t cursor = 0;                   // next item to enqueue
   std::vector<cudaEvent_t> exec_tail;  // last event per exec stream
@@ -641,26 +642,11 @@ int enqueue_subkernels(GemmCall<T>& g, int ui, int order_idx, int ct, int ki0, i
   return PARALIA_OK;
 }
 
-// How many consecutive k tiles of one C tile go into one launch, starting at tile ki0.
-// The split is a function of ki0 alone -- the first launch of every C tile takes one k
-// tile (so that a streamed problem starts computing as soon as one A/B pair has landed),
-// every later launch takes four (the accumulator stays in registers, C makes fewer round
-// trips). Because it depends on nothing else, the arithmetic of a C tile -- and therefore
-// every bit of the result -- is the same whichever GPU runs the tile, however many GPUs
-// take part and wherever A and B live. (A C tile that lives on the executing GPU is
-// updated in place with beta applied by the first launch instead of the last, which
-// rounds differently from a staged tile.)
-template <typename T>
-int kchain_len(const GemmCall<T>& g, int ki0) {
-  static const int forced = [] {
-    const char* e = getenv("PARALIA_KCHAIN");   // experiments only: changes rounding
-    return e ? atoi(e) : 0;
-  }();
-  // a bounded cache keeps only one A and one B tile per launch alive
-  int len = g.evict ? 1 : (forced > 0 ? forced : (ki0 == 0 ? 1 : 4));
-  len = std::min<int>(len, DG_MAX_PARTS);
-  return std::max(len, 1);
-}
+// The k split of a C tile (plan_kchain_len) is a function of the k tile alone, so the
+// arithmetic of a C tile -- and therefore every bit of the result -- is the same whichever
+// GPU runs the tile, however many GPUs take part and wherever A and B live. (A C tile that
+// lives on the executing GPU is updated in place with beta applied by the first launch
+// instead of the last, which rounds differently from a staged tile.)
 
 // The original C tile is needed only by the last launch of its C tile: it is fetched when
 // the launch before that one is enqueued (or with the only launch), so that it rides the
@@ -679,28 +665,7 @@ bool csrc_due(const GemmCall<T>& g, int ki1) {
 // the arithmetic -- and every bit of the result -- is the same as in tile-major order.
 template <typename T>
 void build_items(const GemmCall<T>& g, UnitState& u) {
-  static const int band_env = [] {
-    const char* e = getenv("PARALIA_BAND");
-    return e ? atoi(e) : 0;
-  }();
-  const int n = (int)u.ctiles.size();
-  const int kt = (int)std::max<int64_t>(g.Kt, 1);
-  // about four bands per unit, between 4 and 16 C tiles each (measured best at 4 GPUs)
-  int band = band_env > 0 ? band_env : std::min(16, std::max(4, (n + 3) / 4));
-  if (g.evict) band = 1;   // tile-major: one accumulator alive at a time
-  u.items.clear();
-  for (int b0 = 0; b0 < n; b0 += band) {
-    const int b1 = std::min(n, b0 + band);
-    if (g.Kt == 0) {
-      for (int oi = b0; oi < b1; ++oi) u.items.push_back({oi, 0, 0});
-      continue;
-    }
-    for (int ki0 = 0; ki0 < kt;) {
-      const int ki1 = std::min(kt, ki0 + kchain_len(g, ki0));
-      for (int oi = b0; oi < b1; ++oi) u.items.push_back({oi, ki0, ki1});
-      ki0 = ki1;
-    }
-  }
+  plan_launch_order((int)u.ctiles.size(), (int)g.Kt, g.evict, DG_MAX_PARTS, &u.items);
   u.cursor = 0;
 }
 
@@ -826,23 +791,21 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
   rep->cache_limit = eff_ctl.cache_limit;
 
   g.units.assign(active, UnitState());
-  g.ctile_owner.assign(g.Mt * g.Nt, -1);
   g.a_consumers.assign(g.Mt, std::vector<int>());
   g.b_consumers.assign(g.Nt, std::vector<int>());
-  for (int ui = 0; ui < active; ++ui) {
-    UnitState& u = g.units[ui];
-    u.dev = tuned.active_unit_id_list[ui];
-    rep->subkernels_per_unit[ui] = (int)lists[ui].size();
-    rep->active_unit_score[ui] = 1.0 / active;
-    for (int sk : lists[ui]) {
-      const int ct = sk / kt_for_ids;
-      if (g.ctile_owner[ct] == -1) {
-        g.ctile_owner[ct] = ui;
-        u.ctiles.push_back(ct);
-      } else if (g.ctile_owner[ct] != ui) {
-        cleanup_pins();
-        return fail(PARALIA_ERR_UNSUPPORTED, "distribution split one C tile across units");
-      }
+  {
+    lists.resize(active);
+    std::vector<std::vector<int>> unit_ctiles;
+    if (!plan_unit_ctiles(lists, kt_for_ids, (int)(g.Mt * g.Nt), &unit_ctiles, &g.ctile_owner)) {
+      cleanup_pins();
+      return fail(PARALIA_ERR_UNSUPPORTED, "distribution split one C tile across units");
+    }
+    for (int ui = 0; ui < active; ++ui) {
+      UnitState& u = g.units[ui];
+      u.dev = tuned.active_unit_id_list[ui];
+      rep->subkernels_per_unit[ui] = (int)lists[ui].size();
+      rep->active_unit_score[ui] = 1.0 / active;
+      u.ctiles = unit_ctiles[ui];
     }
   }
   for (int64_t ct = 0; ct < g.Mt * g.Nt; ++ct) {

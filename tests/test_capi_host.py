@@ -238,3 +238,48 @@ def test_predictor_mode_needs_no_gpu_with_a_unit_list(pl, capsys):
                        "32768", "32768", "32768", "-1", "-1", "-1", "-1"])
     capsys.readouterr()
     assert one["T"] == 4096 and 1.9 < one["pred_t"] < 2.2
+
+
+@pytest.mark.parametrize("dims,T,units", [((32768, 32768, 32768), 2048, 8), ((32768, 32768, 32768), 4096, 1),
+                                          ((65536, 65536, 2048), 4096, 2), ((1156, 1412, 1228), 512, 3),
+                                          ((300, 5000, 700), 256, 4), ((4096, 4096, 0), 1024, 2)])
+@pytest.mark.parametrize("bounded", [False, True])
+def test_launch_plan_is_complete_and_static(pl, dims, T, units, bounded):
+    M, N, K = dims
+    items, (d1, d2) = pl.plan_gemm(M, N, K, T, units, bounded)
+    again, _ = pl.plan_gemm(M, N, K, T, units, bounded)
+    assert items == again                                   # a function of its arguments alone
+    Mt, Nt, Kt = -(-M // T), -(-N // T), -(-K // T)
+    owner, g1, g2 = pl.distribute_2d(units, Mt, Nt, max(Kt, 1))
+    assert (d1, d2) == (g1, g2)
+    seen = {}
+    per_tile = {}
+    for (u, mi, ni, k0, k1) in items:
+        assert 0 <= mi < Mt and 0 <= ni < Nt
+        assert owner[(mi * Nt + ni) * max(Kt, 1)] == u      # the unit that owns the C tile runs it
+        per_tile.setdefault((mi, ni), []).append((k0, k1))
+        for k in range(k0, k1):
+            assert (mi, ni, k) not in seen                  # every (mi, ni, ki) exactly once
+            seen[(mi, ni, k)] = u
+    assert len(per_tile) == Mt * Nt
+    if Kt == 0:
+        assert all(v == [(0, 0)] for v in per_tile.values())   # one beta-scaling launch per tile
+        return
+    assert len(seen) == Mt * Nt * Kt
+    # the k split is the same for every C tile and depends on k alone: [0,1), then fours
+    # (ones with a bounded cache), in increasing k
+    want, k = [], 0
+    while k < Kt:
+        step = 1 if (bounded or k == 0) else 4
+        want.append((k, min(Kt, k + step)))
+        k = want[-1][1]
+    assert all(v == want for v in per_tile.values())
+    # round-robin over the units: among the first `active` launches no unit appears twice
+    active = len({u for (u, *_rest) in items})
+    first = [u for (u, *_rest) in items[:active]]
+    assert sorted(first) == list(range(active))
+    if bounded:   # tile-major: a C tile is finished before the unit starts its next one
+        for u in range(active):
+            mine = [(mi, ni) for (uu, mi, ni, _a, _b) in items if uu == u]
+            order = [t for i, t in enumerate(mine) if i == 0 or mine[i - 1] != t]
+            assert len(order) == len(set(order))

@@ -324,3 +324,14 @@ def test_call_waits_for_default_stream_work(pl, orc):
     pl.dgemm("N", "N", M, N, K, 1.0, dA, lda, dB, ldb, 1.0, dC, ldc, locA=0, locB=0, locC=0,
              ctl=pl.make_ctl(T=512, units=[0]))
     assert orc.normwise_rel_err(_host(dC, C.shape), want) <= tol(K)
+
+
+@pytest.mark.parametrize("dims,T", [((1156, 1412, 1228), 256), ((512, 512, 2304), 256)])
+def test_executor_launches_what_the_plan_says(pl, orc, dims, T):
+    # host-resident operands, whole working set cached: one kernel launch per plan item
+    M, N, K = dims
+    A, B, C, lda, ldb, ldc = _case(orc, "N", "N", M, N, K)
+    rep = pl.dgemm("N", "N", M, N, K, 1.0, A, lda, B, ldb, 1.0, C, ldc, ctl=pl.make_ctl(T=T, units=[0]))
+    items, grid = pl.plan_gemm(M, N, K, T, 1)
+    assert rep.kernel_launches == len(items)
+    assert (rep.grid_d1, rep.grid_d2) == grid
