@@ -9,6 +9,8 @@ the build container (needs the reference checkout for the distribution fixture):
 * ``blas_openblas.npz`` -- results of OpenBLAS cblas_dgemm / sgemm / daxpy / ddot (the
   routines the reference uses on its CPU path) on seeded inputs produced by the oracle's
   counter-based generator; inputs are regenerated from the seeds by the tests.
+* ``blas_openblas_dgemv.npz`` -- the same for OpenBLAS cblas_dgemv (kept in a file of its own
+  so that adding it did not rewrite the older fixtures).
 * ``rng_vectors.json`` -- first values of the input generator for fixed seeds.
 """
 import json
@@ -43,6 +45,16 @@ SGEMM_CASES = [
     ("N", "N", 64, 48, 40, 1.0, 0.0, 0),
     ("T", "N", 37, 53, 29, 1.25, 0.75, 3),
     ("N", "T", 33, 65, 17, -0.5, 1.0, 0),
+]
+# (ta, M, N, alpha, beta, extra leading-dimension padding, incx, incy)
+DGEMV_CASES = [
+    ("N", 64, 48, 1.25, 0.75, 0, 1, 1),
+    ("T", 64, 48, 1.25, 0.75, 0, 1, 1),
+    ("N", 37, 53, 1.23, 0.9876, 3, 2, 3),
+    ("T", 37, 53, -0.5, 0.0, 3, 3, 2),
+    ("N", 1, 70, 2.0, -1.0, 0, 1, 1),
+    ("T", 70, 1, 2.0, -1.0, 1, 1, 1),
+    ("N", 513, 257, 1.0, 1.0, 1, 1, 1),
 ]
 L1_CASES = [(1000, 1, 1, -0.5), (777, 2, 3, 1.5), (4096, 1, 1, 0.25), (1, 1, 1, 3.0)]
 
@@ -90,6 +102,26 @@ def gen_blas():
     print("blas fixtures:", len(out))
 
 
+def dgemv_inputs(case):
+    ta, M, N, alpha, beta, pad, incx, incy = case
+    in_len, out_len = (M, N) if ta == "T" else (N, M)
+    A = oracle.matrix_f64(M, N, 42, M + pad)
+    x = oracle.uniform_f64(1 + (in_len - 1) * incx, 43)
+    y = oracle.uniform_f64(1 + (out_len - 1) * incy, 44)
+    return A, x, y
+
+
+def gen_dgemv():
+    out = {}
+    for i, case in enumerate(DGEMV_CASES):
+        ta, M, N, alpha, beta, pad, incx, incy = case
+        A, x, y = dgemv_inputs(case)
+        out[f"dgemv_{i}"] = oracle.openblas_dgemv(ta, alpha, A[:M, :], x[::incx].copy(), beta,
+                                                  y[::incy].copy())
+    np.savez_compressed(OUT / "blas_openblas_dgemv.npz", **out)
+    print("dgemv fixtures:", len(out))
+
+
 def gen_rng():
     vec = {
         "uniform_f64_seed42": [float(v).hex() for v in oracle.uniform_f64(8, 42)],
@@ -103,4 +135,5 @@ def gen_rng():
 if __name__ == "__main__":
     gen_distribution()
     gen_blas()
+    gen_dgemv()
     gen_rng()

@@ -125,3 +125,16 @@ def test_tile_dgemv_invalid_arguments(pl):
         pl.tile_dgemv(0, "N", 4, 4, 1.0, d, 4, d, 1, 0.0, d, 1, None)   # op = N without scratch
     with pytest.raises(pl.ParaliaError):
         pl.tile_dgemv(0, "T", 4, 4, 1.0, d, 4, d, 0, 0.0, d, 1, None)   # zero increment
+
+
+def test_dgemv_host_vs_openblas_golden(pl, orc, golden_dir):
+    import pathlib, sys
+    sys.path.insert(0, str(pathlib.Path(__file__).resolve().parent / "golden"))
+    from gen_golden import DGEMV_CASES, dgemv_inputs
+    gold = np.load(golden_dir / "blas_openblas_dgemv.npz")
+    for i, case in enumerate(DGEMV_CASES):
+        ta, M, N, alpha, beta, pad, incx, incy = case
+        A, x, y = dgemv_inputs(case)
+        pl.dgemv(ta, M, N, alpha, A, M + pad, x, incx, beta, y, incy, ctl=pl.make_ctl(T=64, units=[0]))
+        in_len = M if ta == "T" else N
+        assert orc.normwise_rel_err(y[::incy], gold[f"dgemv_{i}"]) <= 8 * in_len * EPS64, case

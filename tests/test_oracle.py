@@ -130,3 +130,18 @@ def test_dgemv_oracle_vs_openblas_live(orc, ta, dims):
     want = orc.openblas_dgemv(ta, 1.23, A[:M, :], x, 0.9876, y)
     orc.dgemv(ta, M, N, 1.23, A, M + 3, x, 1, 0.9876, y, 1)
     assert orc.normwise_rel_err(y, want) <= 8 * in_len * EPS64
+
+
+def test_dgemv_oracle_vs_openblas_golden(orc, golden_dir):
+    from gen_golden import DGEMV_CASES, dgemv_inputs
+    gold = np.load(golden_dir / "blas_openblas_dgemv.npz")
+    for i, case in enumerate(DGEMV_CASES):
+        ta, M, N, alpha, beta, pad, incx, incy = case
+        A, x, y = dgemv_inputs(case)
+        before = y.copy()
+        orc.dgemv(ta, M, N, alpha, A, M + pad, x, incx, beta, y, incy)
+        in_len = M if ta == "T" else N
+        assert orc.normwise_rel_err(y[::incy], gold[f"dgemv_{i}"]) <= 8 * in_len * EPS64, case
+        if incy > 1:      # elements between the strides are untouched
+            mask = np.ones(len(y), bool); mask[::incy] = False
+            assert np.array_equal(y[mask], before[mask])
