@@ -62,13 +62,40 @@ def _ok(status: int, what: str) -> None:
         raise RuntimeError(f"{what} failed with cuBLAS status {status}")
 
 
+class ComparatorRefused(ValueError):
+    """The requested comparator run would hand a vendor kernel memory of another GPU."""
+
+
+def check_xt_placement(dev_ids, locs) -> None:
+    """cuBLASXt runs vendor GEMM kernels on every GPU of ``dev_ids``. Those kernels must never
+    be given an operand that lives on a different GPU, so a run is allowed only if every
+    operand is in host memory, or there is exactly one GPU and every GPU-resident operand
+    lives on it. Anything else raises ``ComparatorRefused`` before any CUDA call."""
+    devs = list(dev_ids)
+    if not devs:
+        raise ComparatorRefused("empty device list")
+    on_gpu = [int(l) for l in locs if int(l) >= 0]
+    if not on_gpu:
+        return
+    if len(devs) > 1:
+        raise ComparatorRefused(
+            f"cuBLASXt on {len(devs)} GPUs needs all three operands in host memory; "
+            f"operand locations were {tuple(int(l) for l in locs)}")
+    if any(l != devs[0] for l in on_gpu):
+        raise ComparatorRefused(
+            f"cuBLASXt on GPU {devs[0]} cannot take an operand that lives on another GPU; "
+            f"operand locations were {tuple(int(l) for l in locs)}")
+
+
 def cublasxt_gemm(elem_size: int, TransA: str, TransB: str, M: int, N: int, K: int, alpha: float,
                   A: int, ldA: int, B: int, ldB: int, beta: float, Cm: int, ldC: int,
-                  T: int = 0, dev_ids=(0,), pinning: bool = True) -> float:
+                  T: int = 0, dev_ids=(0,), pinning: bool = True, locs=(-1, -1, -1)) -> float:
     """One blocking cublasXt{D,S}gemm on raw pointers (host or device); returns wall seconds
     of the call including handle set-up, as the reference's wrapper does. ``pinning`` =
     False for operands that are already page-locked (asking the library to pin them again
-    makes the call fail with CUBLAS_STATUS_INVALID_VALUE on this toolkit)."""
+    makes the call fail with CUBLAS_STATUS_INVALID_VALUE on this toolkit). ``locs`` are the
+    location ids of A, B and C (-1 host, else the GPU): see ``check_xt_placement``."""
+    check_xt_placement(dev_ids, locs)
     lib = cublas()
     if T <= 0:    # the reference's choice when it validates (dgemm_runner.cpp:97)
         T = int(min(min(M, N, K) // 2, CBLASXT_MAX_SAFE_TILE))
