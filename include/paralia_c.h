@@ -62,6 +62,8 @@ typedef struct paralia_ctl {
 #define PARALIA_FLAG_NO_PEER_FETCH 1  /* every GPU fetches host tiles itself            */
 #define PARALIA_FLAG_KEEP_PINNED   2  /* leave host operands registered after the call  */
 #define PARALIA_FLAG_NO_METADATA_REUSE 4 /* rebuild the plan even for a known signature */
+#define PARALIA_FLAG_BETA_ZERO 8      /* PARALiA_autotune_gemm only (it takes no beta): model
+                                         the call with beta == 0, i.e. C is not fetched  */
 
 /*
  * What a call did: the POD form of the ATC object the reference returns
@@ -90,6 +92,11 @@ typedef struct paralia_report {
   int64_t kernel_launches;   /* launches of this library's own kernels          */
   int32_t metadata_reused;   /* 1 if the plan came from the signature cache     */
   int32_t grid_d1, grid_d2;  /* device grid D1_parts x D2_parts                 */
+  /* phases of device_ms (GEMM routines; 0 elsewhere), each the max over the GPUs used,
+   * measured from the call's start event:                                      */
+  double  fill_ms;           /* until the first tile kernel starts              */
+  double  exec_end_ms;       /* until the last tile kernel ends                 */
+  double  h2d_end_ms;        /* until the last host -> GPU copy ends            */
 } paralia_report;
 
 /* ---- library life cycle ---------------------------------------------------------- */
@@ -258,6 +265,22 @@ int PARALiA_fill_f32(float* ptr, int64_t n, uint64_t seed, int dist, int loc);
 int PARALiA_autotune_gemm(int elem_size, char TransA, char TransB,
                           int64_t M, int64_t N, int64_t K, int locA, int locB, int locC,
                           const paralia_ctl* ctl, paralia_report* out);
+/* Level-1 counterpart (ModelLvl1.cpp:19-144 with Autotuner.cpp:279-560): unit set, tile
+ * length and predicted seconds of DAXPY (is_dot == 0) or DDOT on vectors of N doubles at
+ * locx / locy, from the measured Daxpy / Ddot tile tables and the shared host-link model. */
+int PARALiA_autotune_vec(int is_dot, int64_t N, int locx, int locy, const paralia_ctl* ctl,
+                         paralia_report* out);
+/* The shared host-link model (Autotuner/src/CoModel.cpp:120-140 t_com_predict_shared,
+ * LinkMap.cpp:121-269 update_link_shared_weights, restated for one NVSwitch box): seconds to
+ * move `bytes` over the host link of GPU `dev` (to_gpu != 0: host -> GPU) while n_active
+ * GPUs use their host links in the same direction and, if both_directions != 0, the other
+ * direction is busy too. active_devs (may be NULL) names those GPUs, for the pairwise
+ * "Slowdown" factors of the link files; the aggregate table caps the result.
+ * *defer_writebacks (may be NULL) receives 1 if, with n_active GPUs, the executor holds C
+ * write-backs until a GPU's input stream has drained. */
+int PARALiA_model_host_link(int dev, int to_gpu, int64_t bytes, int n_active, int both_directions,
+                            const int32_t* active_devs, int n_devs, double* seconds,
+                            int32_t* defer_writebacks);
 /* Tile-size score of one candidate T (Autotuner.cpp:571-603); slowdowns[6]. */
 int PARALiA_tile_slowdowns(int64_t M, int64_t N, int64_t K, int64_t T, int active_units,
                            double* slowdowns);
@@ -291,8 +314,22 @@ int PARALiA_bench_dmma_peak(int dev, int shape, int iters, double* tflops);
 /* Time `reps` launches of the tile DGEMM on square T; returns mean seconds. */
 int PARALiA_bench_tile_dgemm(int dev, char TransA, char TransB, int64_t T, int reps,
                              double* mean_s);
+/* The same with launches of T x T x (chain*T), the shape the executor launches when it
+ * chains k tiles of one C tile (spread over up to four streams as the executor does); returns
+ * mean seconds per k tile. chain = 4 is what the shipped tile tables hold. */
+int PARALiA_bench_tile_dgemm_chain(int dev, char TransA, char TransB, int64_t T, int chain,
+                                   int reps, double* mean_s);
 /* Same for the FP32 kernel: operands are packed once, only the GEMM kernel is timed. */
 int PARALiA_bench_tile_sgemm(int dev, int64_t T, int reps, double* mean_s);
+/* Level-1 tile kernels on device-resident vectors of N doubles (reference:
+ * Database_builder/CuCuBLAS/src/daxpy_microbench.cu:26-231, ddot_microbench.cu:26-228);
+ * mean seconds per tile. */
+int PARALiA_bench_tile_daxpy(int dev, int64_t N, int reps, double* mean_s);
+int PARALiA_bench_tile_ddot(int dev, int64_t N, int reps, double* mean_s);
+/* All host links of GPUs 0..ngpu-1 at once, `reps` pinned copies of `bytes` each per GPU
+ * and direction. mode 0: host -> GPU only, 1: GPU -> host only, 2: both directions together.
+ * *gbs receives the aggregate GB/s per direction. No counterpart in the reference. */
+int PARALiA_bench_host_aggregate(int ngpu, int mode, int64_t bytes, int reps, double* gbs);
 /* Time a strided 2-D tile copy dim x dim doubles src_loc -> dst_loc; mean seconds. */
 int PARALiA_bench_link(int dst_loc, int src_loc, int64_t dim, int reps, double* mean_s);
 

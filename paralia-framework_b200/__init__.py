@@ -25,6 +25,7 @@ LOC_AUTO = -100
 FLAG_NO_PEER_FETCH = 1
 FLAG_KEEP_PINNED = 2
 FLAG_NO_METADATA_REUSE = 4
+FLAG_BETA_ZERO = 8          # autotune_gemm only: model the call with beta == 0
 
 OK = 0
 ERR_INVALID_ARG = 1
@@ -86,6 +87,9 @@ class Report(C.Structure):
         ("metadata_reused", C.c_int32),
         ("grid_d1", C.c_int32),
         ("grid_d2", C.c_int32),
+        ("fill_ms", C.c_double),
+        ("exec_end_ms", C.c_double),
+        ("h2d_end_ms", C.c_double),
     ]
 
     def as_dict(self) -> dict:
@@ -102,6 +106,7 @@ class Report(C.Structure):
             "p2p_bytes": self.p2p_bytes, "d2d_bytes": self.d2d_bytes,
             "kernel_launches": self.kernel_launches, "grid": (self.grid_d1, self.grid_d2),
             "metadata_reused": self.metadata_reused,
+            "fill_ms": self.fill_ms, "exec_end_ms": self.exec_end_ms, "h2d_end_ms": self.h2d_end_ms,
         }
 
 
@@ -158,7 +163,15 @@ SIGNATURES = {
     "PARALiA_load_database": (C.c_int, [C.c_char_p]),
     "PARALiA_bench_dmma_peak": (C.c_int, [C.c_int, C.c_int, C.c_int, C.POINTER(_dbl)]),
     "PARALiA_bench_tile_dgemm": (C.c_int, [C.c_int, _chr, _chr, _i64, C.c_int, C.POINTER(_dbl)]),
+    "PARALiA_bench_tile_dgemm_chain": (C.c_int, [C.c_int, _chr, _chr, _i64, C.c_int, C.c_int,
+                                                 C.POINTER(_dbl)]),
     "PARALiA_bench_tile_sgemm": (C.c_int, [C.c_int, _i64, C.c_int, C.POINTER(_dbl)]),
+    "PARALiA_bench_tile_daxpy": (C.c_int, [C.c_int, _i64, C.c_int, C.POINTER(_dbl)]),
+    "PARALiA_bench_tile_ddot": (C.c_int, [C.c_int, _i64, C.c_int, C.POINTER(_dbl)]),
+    "PARALiA_bench_host_aggregate": (C.c_int, [C.c_int, C.c_int, _i64, C.c_int, C.POINTER(_dbl)]),
+    "PARALiA_autotune_vec": (C.c_int, [C.c_int, _i64, C.c_int, C.c_int, _ctl_p, _rep_p]),
+    "PARALiA_model_host_link": (C.c_int, [C.c_int, C.c_int, _i64, C.c_int, C.c_int, C.POINTER(_i32),
+                                          C.c_int, C.POINTER(_dbl), C.POINTER(_i32)]),
     "PARALiA_bench_link": (C.c_int, [C.c_int, C.c_int, _i64, C.c_int, C.POINTER(_dbl)]),
     "PARALiA_bench_link_overlap": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, _i64, C.c_int,
                                              C.POINTER(_dbl), C.POINTER(_dbl)]),
@@ -411,6 +424,27 @@ def autotune_gemm(elem_size, TransA, TransB, M, N, K, locA, locB, locC,
     return rep
 
 
+def autotune_vec(is_dot: bool, N, locx, locy, ctl: Ctl | None = None) -> Report:
+    """Reference: ATC::autotune_problem for the level-1 models (ModelLvl1.cpp:19-144)."""
+    rep = Report()
+    _check(lib().PARALiA_autotune_vec(int(bool(is_dot)), N, locx, locy,
+                                      C.byref(ctl) if ctl is not None else None, C.byref(rep)))
+    return rep
+
+
+def model_host_link(dev, to_gpu: bool, nbytes, n_active, both_directions=False, active_devs=None):
+    """Seconds the shared host-link model predicts, and whether write-backs are deferred with
+    ``n_active`` GPUs. Reference: t_com_predict_shared (CoModel.cpp:120-140)."""
+    sec, defer = _dbl(), _i32()
+    arr, n = None, 0
+    if active_devs is not None:
+        n = len(active_devs)
+        arr = (_i32 * max(n, 1))(*active_devs)
+    _check(lib().PARALiA_model_host_link(dev, int(bool(to_gpu)), int(nbytes), n_active,
+                                         int(bool(both_directions)), arr, n, C.byref(sec), C.byref(defer)))
+    return sec.value, bool(defer.value)
+
+
 def tile_slowdowns(M, N, K, T, units) -> list[float]:
     """Reference: ATC::get_T_slowdowns (Autotuner.cpp:571-603)."""
     sl = (C.c_double * 6)()
@@ -448,6 +482,31 @@ def load_database(path: str) -> None:
 def bench_dmma_peak(dev=0, shape=1688, iters=20000) -> float:
     v = C.c_double()
     _check(lib().PARALiA_bench_dmma_peak(dev, shape, iters, C.byref(v)))
+    return v.value
+
+
+def bench_tile_dgemm_chain(dev, TransA, TransB, T, chain, reps) -> float:
+    v = _dbl()
+    _check(lib().PARALiA_bench_tile_dgemm_chain(dev, _c(TransA), _c(TransB), T, chain, reps, C.byref(v)))
+    return v.value
+
+
+def bench_tile_daxpy(dev, N, reps) -> float:
+    v = _dbl()
+    _check(lib().PARALiA_bench_tile_daxpy(dev, N, reps, C.byref(v)))
+    return v.value
+
+
+def bench_tile_ddot(dev, N, reps) -> float:
+    v = _dbl()
+    _check(lib().PARALiA_bench_tile_ddot(dev, N, reps, C.byref(v)))
+    return v.value
+
+
+def bench_host_aggregate(ngpu, mode, nbytes, reps) -> float:
+    """Aggregate GB/s per direction; mode 0 host->GPU, 1 GPU->host, 2 both together."""
+    v = _dbl()
+    _check(lib().PARALiA_bench_host_aggregate(ngpu, mode, int(nbytes), reps, C.byref(v)))
     return v.value
 
 

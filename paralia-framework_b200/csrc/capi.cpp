@@ -341,6 +341,7 @@ int PARALiA_autotune_gemm(int elem_size, char TransA, char TransB, int64_t M, in
   in.M = M; in.N = N; in.K = K;
   in.locA = locA; in.locB = locB; in.locC = locC;
   in.func = elem_size == 8 ? "Dgemm" : "Sgemm";
+  in.beta_nonzero = !(ctl && (ctl->flags & PARALIA_FLAG_BETA_ZERO));
   return autotune_gemm(in, ngpu, ctl, out);
 }
 
@@ -385,8 +386,35 @@ int PARALiA_plan_gemm(int64_t M, int64_t N, int64_t K, int64_t T, int units, int
   if (!plan_unit_ctiles(lists, kt_for_ids, (int)(Mt * Nt), &ctiles, &owner))
     return fail(PARALIA_ERR_UNSUPPORTED, "distribution split one C tile across units");
   std::vector<std::vector<LaunchItem>> per_unit(active);
-  for (int u = 0; u < active; ++u)
-    plan_launch_order((int)ctiles[u].size(), (int)Kt, bounded_cache != 0, DG_MAX_PARTS, &per_unit[u]);
+  // band sizes as the executor derives them for FP64 operands that all live in host memory
+  // (the streaming case), from the calibration database that is loaded now
+  if (model_db().link.empty()) reset_database_defaults(std::max(units, 1));
+  GemmModelInput mi;
+  mi.esz = 8; mi.ta = 'N'; mi.tb = 'N';
+  mi.M = M; mi.N = N; mi.K = std::max<int64_t>(K, 1);
+  mi.locA = mi.locB = mi.locC = -1;
+  mi.beta_nonzero = true;
+  mi.func = "Dgemm";
+  for (int u = 0; u < active; ++u) {
+    int row_len = 0;
+    for (int ct : ctiles[u]) {
+      if (ct / Nt != ctiles[u][0] / Nt) break;
+      ++row_len;
+    }
+    int a_sh = 0, b_sh = 0;   // units that own tiles of this unit's first tile row / column
+    if (!ctiles[u].empty()) {
+      std::vector<char> in_row(active, 0), in_col(active, 0);
+      for (int64_t ct = 0; ct < Mt * Nt; ++ct) {
+        if (ct / Nt == ctiles[u][0] / Nt) in_row[owner[ct]] = 1;
+        if (ct % Nt == ctiles[u][0] % Nt) in_col[owner[ct]] = 1;
+      }
+      for (int v = 0; v < active; ++v) { a_sh += in_row[v]; b_sh += in_col[v]; }
+    }
+    const BandHints hints = band_hints(mi, T, u, active, std::max(a_sh, 1), std::max(b_sh, 1), row_len);
+    std::vector<int> bands;
+    plan_band_sizes((int)ctiles[u].size(), (int)Kt, bounded_cache != 0, hints, &bands);
+    plan_launch_order(bands, (int)Kt, bounded_cache != 0, DG_MAX_PARTS, &per_unit[u]);
+  }
   // the executor walks the units round-robin, one launch per turn
   int64_t n = 0;
   std::vector<size_t> cursor(active, 0);
@@ -482,23 +510,33 @@ int PARALiA_bench_dmma_peak(int dev, int shape, int iters, double* tflops) {
 
 int PARALiA_bench_tile_dgemm(int dev, char TransA, char TransB, int64_t T, int reps,
                              double* mean_s) {
+  return PARALiA_bench_tile_dgemm_chain(dev, TransA, TransB, T, 1, reps, mean_s);
+}
+
+int PARALiA_bench_tile_dgemm_chain(int dev, char TransA, char TransB, int64_t T, int chain,
+                                   int reps, double* mean_s) {
   // The tile time the model needs is the one the executor sees: tiles of different C
   // accumulators run on several exec streams at once, so the partial last wave of one tile
   // is filled by the next. `reps` tiles are therefore spread round-robin over up to four
   // streams (one C per stream) and the mean is total time / reps; reps = 1 times one tile
   // alone, as the reference's microbenchmark does (dgemm_microbench.cu:125-187).
-  if (!mean_s || reps <= 0 || T <= 0) return fail(PARALIA_ERR_INVALID_ARG, "bad bench arguments");
+  // A launch of the executor usually covers a chain of k tiles of one C tile (four after the
+  // first): `chain` makes each timed launch T x T x (chain*T) and the result is the time
+  // per k tile, i.e. per T x T x T subkernel, inside such a launch.
+  if (!mean_s || reps <= 0 || T <= 0 || chain <= 0 || chain > 16)
+    return fail(PARALIA_ERR_INVALID_ARG, "bad bench arguments");
+  const int64_t Kc = T * chain;
   DeviceGuard guard;
   PL_TRY(setup_device(dev));
   DeviceCtx& dc = Runtime::get().dev(dev);
   const int S = std::min(reps, 4);
   const size_t n = (size_t)T * T;
   double *A = nullptr, *B = nullptr, *C = nullptr;
-  PL_CUDA(cudaMalloc(&A, n * 8));
-  PL_CUDA(cudaMalloc(&B, n * 8));
+  PL_CUDA(cudaMalloc(&A, n * 8 * chain));
+  PL_CUDA(cudaMalloc(&B, n * 8 * chain));
   PL_CUDA(cudaMalloc(&C, n * 8 * S));
-  PL_CUDA(launch_fill_f64(A, n, 42, 0, nullptr));
-  PL_CUDA(launch_fill_f64(B, n, 43, 0, nullptr));
+  PL_CUDA(launch_fill_f64(A, n * chain, 42, 0, nullptr));
+  PL_CUDA(launch_fill_f64(B, n * chain, 43, 0, nullptr));
   PL_CUDA(launch_fill_f64(C, n * S, 44, 0, nullptr));
   PL_CUDA(cudaDeviceSynchronize());
   cudaEvent_t e0, e1, join[4] = {nullptr, nullptr, nullptr, nullptr};
@@ -506,15 +544,16 @@ int PARALiA_bench_tile_dgemm(int dev, char TransA, char TransB, int64_t T, int r
   PL_CUDA(cudaEventCreate(&e1));
   for (int s = 1; s < S; ++s) PL_CUDA(cudaEventCreateWithFlags(&join[s], cudaEventDisableTiming));
   int rc = PARALIA_OK;
+  const int64_t lda = norm_t(TransA) ? Kc : T, ldb = norm_t(TransB) ? T : Kc;
   for (int i = 0; i < 2 && rc == PARALIA_OK; ++i)
-    rc = PARALiA_tile_dgemm(dev, dc.exec[0], TransA, TransB, T, T, T, 1.0, A, T, B, T, 0.5, C, T);
+    rc = PARALiA_tile_dgemm(dev, dc.exec[0], TransA, TransB, T, T, Kc, 1.0, A, lda, B, ldb, 0.5, C, T);
   if (rc == PARALIA_OK) {
     PL_CUDA(cudaSetDevice(dev));
     PL_CUDA(cudaDeviceSynchronize());
     PL_CUDA(cudaEventRecord(e0, dc.exec[0]));
     for (int s = 1; s < S; ++s) PL_CUDA(cudaStreamWaitEvent(dc.exec[s], e0, 0));
     for (int i = 0; i < reps && rc == PARALIA_OK; ++i)
-      rc = PARALiA_tile_dgemm(dev, dc.exec[i % S], TransA, TransB, T, T, T, 1.0, A, T, B, T, 0.5,
+      rc = PARALiA_tile_dgemm(dev, dc.exec[i % S], TransA, TransB, T, T, Kc, 1.0, A, lda, B, ldb, 0.5,
                               C + (size_t)(i % S) * n, T);
     PL_CUDA(cudaSetDevice(dev));
     for (int s = 1; s < S; ++s) {
@@ -525,7 +564,7 @@ int PARALiA_bench_tile_dgemm(int dev, char TransA, char TransB, int64_t T, int r
     PL_CUDA(cudaEventSynchronize(e1));
     float ms = 0.f;
     PL_CUDA(cudaEventElapsedTime(&ms, e0, e1));
-    *mean_s = ms * 1e-3 / reps;
+    *mean_s = ms * 1e-3 / reps / chain;
   }
   cudaEventDestroy(e0);
   cudaEventDestroy(e1);

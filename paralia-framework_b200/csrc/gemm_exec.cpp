@@ -40,6 +40,16 @@ namespace {
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 inline int64_t round_up(int64_t a, int64_t b) { return ceil_div(a, b) * b; }
 
+// Which unit pulls a host-resident A tile (mi, ki) or B tile (ki, ni) over its host link
+// and forwards it to the other consumers. `cons` are the consumers of the tile row / column
+// in grid order, `first` the first tile row / column with the same consumers, `lead` the
+// grid row (A) or grid column + 1 (B) of that set. The rotation by (local index + k) spreads
+// a unit's fetches over k; the lead term makes the tiles that the very first launches need
+// (local index 0, k 0) come over different host links on a device grid of 2 x 2 and more.
+inline int rotating_home(int n_cons, int lead, int64_t local, int64_t ki) {
+  return (int)(((int64_t)lead + local + ki) % n_cons);
+}
+
 struct OperandDesc {
   const void* ptr = nullptr;
   int64_t ld = 0;
@@ -83,6 +93,7 @@ struct UnitState {
   std::vector<Item> items;
   size_t cursor = 0;                   // next item to enqueue
   std::vector<cudaEvent_t> exec_tail;  // last event per exec stream
+  bool first_exec_marked = false;      // the call's first kernel start has been recorded
   cudaEvent_t h2d_tail = nullptr, p2p_tail = nullptr, pack_tail = nullptr;
 };
 
@@ -111,6 +122,26 @@ struct GemmCall {
   std::vector<int> ctile_owner;             // C tile -> unit index
   std::vector<std::vector<int>> a_consumers; // per tile-row mi: units that read A(mi,*)
   std::vector<std::vector<int>> b_consumers; // per tile-col ni: units that read B(*,ni)
+  std::vector<int> a_first, b_first;          // first tile row / column with the same consumers
+  int grid_d1 = 1, grid_d2 = 1;
+
+  // In-process mode: index into a_consumers[mi] / b_consumers[ni] of the tile's home unit.
+  int home_index(bool is_a, int64_t i0, int64_t i1) const {
+    if (is_a) {
+      const std::vector<int>& cons = a_consumers[i0];
+      return rotating_home((int)cons.size(), cons[0] / std::max(grid_d2, 1), i0 - a_first[i0], i1);
+    }
+    const std::vector<int>& cons = b_consumers[i1];
+    return rotating_home((int)cons.size(), cons[0] % std::max(grid_d2, 1) + 1, i1 - b_first[i1], i0);
+  }
+  // Group mode: rank that is the home of a shared tile of this rank's own panels.
+  int group_home(bool is_a, int64_t i0, int64_t i1) const {
+    int d1, d2;
+    grp->grid(&d1, &d2);
+    const int me = grp->rank(), gr = me / d2, gc = me % d2;
+    if (is_a) return gr * d2 + rotating_home(d2, gr, i0, i1);
+    return rotating_home(d1, gc + 1, i1, i0) * d2 + gc;
+  }
   paralia_report* rep = nullptr;
   static constexpr int esz = (int)sizeof(T);
 
@@ -314,11 +345,9 @@ int ensure_input_f32(GemmCall<T>& g, int ui, bool is_a, int64_t i0, int64_t i1) 
   PL_CUDA(cudaSetDevice(u.dev));
   DeviceCtx& dc = rt.dev(u.dev);
   if (g.grp && op.loc == -1 && (is_a ? g.share_a : g.share_b)) {
-    int d1, d2;
-    g.grp->grid(&d1, &d2);
-    const int me = g.grp->rank(), gr = me / d2, gc = me % d2;
+    const int me = g.grp->rank();
     const int slot = is_a ? (int)tid : g.nA + (int)tid;
-    const int home = is_a ? gr * d2 + (int)((i0 + i1) % d2) : (int)((i0 + i1) % d1) * d2 + gc;
+    const int home = g.group_home(is_a, i0, i1);
     if (home == me) {
       r.block = slot;
       PL_TRY(rt.get_event(u.dev, &r.ready));
@@ -348,7 +377,7 @@ int ensure_input_f32(GemmCall<T>& g, int ui, bool is_a, int64_t i0, int64_t i1) 
   int home = ui;
   if (op.loc == -1 && !g.grp) {
     const std::vector<int>& cons = is_a ? g.a_consumers[i0] : g.b_consumers[i1];
-    if (g.peer_fetch && cons.size() > 1) home = cons[(size_t)(i0 + i1) % cons.size()];
+    if (g.peer_fetch && cons.size() > 1) home = cons[g.home_index(is_a, i0, i1)];
     if (home != ui && !rt.peer_ok(u.dev, g.units[home].dev)) home = ui;
   }
   if (home == ui) {
@@ -392,11 +421,9 @@ int ensure_input(GemmCall<T>& g, int ui, bool is_a, int64_t i0, int64_t i1) {
     // Group mode: the tile is shared between the processes of this rank's grid row (A) or
     // column (B). Blocks and event slots are fixed functions of the tile so that every
     // process knows where a peer keeps it.
-    int d1, d2;
-    g.grp->grid(&d1, &d2);
-    const int me = g.grp->rank(), gr = me / d2, gc = me % d2;
+    const int me = g.grp->rank();
     const int slot = is_a ? (int)tid : g.nA + (int)tid;
-    const int home = is_a ? gr * d2 + (int)((i0 + i1) % d2) : (int)((i0 + i1) % d1) * d2 + gc;
+    const int home = g.group_home(is_a, i0, i1);
     if (home == me) {
       r.block = slot;
       PL_TRY(rt.get_event(u.dev, &r.ready));
@@ -433,7 +460,7 @@ int ensure_input(GemmCall<T>& g, int ui, bool is_a, int64_t i0, int64_t i1) {
     // others take it from the home's cache over NVLink.
     const std::vector<int>& cons = is_a ? g.a_consumers[i0] : g.b_consumers[i1];
     int home = ui;
-    if (g.peer_fetch && cons.size() > 1) home = cons[(size_t)(i0 + i1) % cons.size()];
+    if (g.peer_fetch && cons.size() > 1) home = cons[g.home_index(is_a, i0, i1)];
     if (home != ui && !rt.peer_ok(u.dev, g.units[home].dev)) home = ui;
     if (home == ui) {
       PL_TRY(copy_tile_in(g, u, r.block, t.src, op.ld, t, dc.h2d, &g.rep->h2d_bytes));
@@ -606,6 +633,11 @@ int enqueue_subkernels(GemmCall<T>& g, int ui, int order_idx, int ct, int ki0, i
       }
     }
   }
+  if (!u.first_exec_marked) {
+    // lands when everything the first launch waits for has arrived
+    PL_CUDA(cudaEventRecord(dc.t_first_exec, es));
+    u.first_exec_marked = true;
+  }
   if constexpr (IS_F64) {
     const bool a_kc = g.A.trans, b_kc = !g.B.trans;
     const CUtensorMap& mapA = a_native ? u.map_a_native : (a_kc ? u.map_slab_kc : u.map_slab_mn);
@@ -664,8 +696,28 @@ bool csrc_due(const GemmCall<T>& g, int ki1) {
 // write back while the next band computes. The k split of each C tile is untouched, so
 // the arithmetic -- and every bit of the result -- is the same as in tile-major order.
 template <typename T>
-void build_items(const GemmCall<T>& g, UnitState& u) {
-  plan_launch_order((int)u.ctiles.size(), (int)g.Kt, g.evict, DG_MAX_PARTS, &u.items);
+void build_items(const GemmCall<T>& g, UnitState& u, const GemmModelInput& model_in) {
+  // tiles of the unit's first tile row: the unit's list is row-major over its block
+  int row_len = 0;
+  for (int ct : u.ctiles) {
+    if (ct / g.Nt != u.ctiles[0] / g.Nt) break;
+    ++row_len;
+  }
+  int a_sharers = 1, b_sharers = 1, pulling = (int)g.units.size();
+  if (g.grp) {
+    int d1, d2;
+    g.grp->grid(&d1, &d2);
+    a_sharers = g.share_a ? d2 : 1;
+    b_sharers = g.share_b ? d1 : 1;
+    pulling = g.grp->world();
+  } else if (g.peer_fetch && !u.ctiles.empty()) {
+    a_sharers = (int)g.a_consumers[u.ctiles[0] / g.Nt].size();
+    b_sharers = (int)g.b_consumers[u.ctiles[0] % g.Nt].size();
+  }
+  const BandHints hints = band_hints(model_in, g.Tt, u.dev, pulling, a_sharers, b_sharers, row_len);
+  std::vector<int> bands;
+  plan_band_sizes((int)u.ctiles.size(), (int)g.Kt, g.evict, hints, &bands);
+  plan_launch_order(bands, (int)g.Kt, g.evict, DG_MAX_PARTS, &u.items);
   u.cursor = 0;
 }
 
@@ -816,6 +868,13 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
     add(g.a_consumers[ct / g.Nt], ui);
     add(g.b_consumers[ct % g.Nt], ui);
   }
+  g.grid_d1 = d1; g.grid_d2 = d2;
+  g.a_first.assign(g.Mt, 0);
+  g.b_first.assign(g.Nt, 0);
+  for (int64_t mi = 1; mi < g.Mt; ++mi)
+    g.a_first[mi] = g.a_consumers[mi] == g.a_consumers[mi - 1] ? g.a_first[mi - 1] : (int)mi;
+  for (int64_t ni = 1; ni < g.Nt; ++ni)
+    g.b_first[ni] = g.b_consumers[ni] == g.b_consumers[ni - 1] ? g.b_first[ni - 1] : (int)ni;
 
   // ------------------------------ resources ------------------------------
   double alloc_ms = 0.0;
@@ -949,15 +1008,16 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
     cudaStreamWaitEvent(dc.pack, dc.t_begin, 0);
     cudaStreamWaitEvent(dc.d2h, dc.t_begin, 0);
   }
-  for (int ui = 0; ui < active; ++ui) build_items(g, g.units[ui]);
+  for (int ui = 0; ui < active; ++ui) build_items(g, g.units[ui], mi_in);
   // With four or more GPUs pulling from the host at once, this class of host delivers far
   // less in both directions together than in one direction alone (measured on an
   // 8 x B200 box: 185 GB/s host->GPU alone, 63 + 63 GB/s with GPU->host traffic running),
   // so C tiles are written back only after the unit's input stream has drained; with
-  // fewer GPUs the two directions overlap well and tiles go back as they finish.
+  // fewer GPUs the two directions overlap well and tiles go back as they finish. The
+  // decision is read off the calibration database's host aggregate table.
   {
     const char* e = getenv("PARALIA_DEFER_WB");
-    g.defer_wb = e ? atoi(e) != 0 : (grp ? grp->world() : active) >= 4;
+    g.defer_wb = e ? atoi(e) != 0 : defer_writebacks(grp ? grp->world() : active);
     if (g.evict) g.defer_wb = false;   // blocks are needed back as soon as a tile is home
   }
   if (grp) {
@@ -1020,6 +1080,9 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
     cudaSetDevice(u.dev);
     if (rc == PARALIA_OK) {
       for (int s = 0; s < g.exec_streams; ++s)
+        if (u.exec_tail[s]) cudaEventRecord(dc.t_exec_end[s], dc.exec[s]);
+      cudaEventRecord(dc.t_h2d_end, dc.h2d);
+      for (int s = 0; s < g.exec_streams; ++s)
         if (u.exec_tail[s]) cudaStreamWaitEvent(dc.d2h, u.exec_tail[s], 0);
       if (u.h2d_tail) cudaStreamWaitEvent(dc.d2h, u.h2d_tail, 0);
       if (u.p2p_tail) cudaStreamWaitEvent(dc.d2h, u.p2p_tail, 0);
@@ -1039,6 +1102,14 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
       float ms = 0.f;
       if (cudaEventElapsedTime(&ms, dc.t_begin, dc.t_end) == cudaSuccess)
         dev_ms = std::max(dev_ms, (double)ms);
+      if (u.first_exec_marked && cudaEventElapsedTime(&ms, dc.t_begin, dc.t_first_exec) == cudaSuccess)
+        rep->fill_ms = std::max(rep->fill_ms, (double)ms);
+      for (int s = 0; s < g.exec_streams; ++s)
+        if (u.exec_tail[s] && cudaEventElapsedTime(&ms, dc.t_begin, dc.t_exec_end[s]) == cudaSuccess)
+          rep->exec_end_ms = std::max(rep->exec_end_ms, (double)ms);
+      if (cudaEventElapsedTime(&ms, dc.t_begin, dc.t_h2d_end) == cudaSuccess)
+        rep->h2d_end_ms = std::max(rep->h2d_end_ms, (double)ms);
+      cudaGetLastError();
     }
   }
   if (rc == PARALIA_OK)

@@ -11,6 +11,7 @@
 #include <vector>
 
 #include "level1.cuh"
+#include "autotune.hpp"
 #include "runtime.hpp"
 
 namespace paralia {
@@ -89,30 +90,23 @@ int run_level1(bool is_dot, int64_t N, double alpha, const double* x, int64_t in
   if (rc != PARALIA_OK) { cleanup(); return rc; }
   rep->pin_ms = pin_ms;
 
-  // ---- units: a vector that already sits on a GPU is processed there; host vectors
-  // are spread over the GPUs the caller names, else over all of them (each brings its
-  // own host link).
+  // ---- units and tile length from the model (ModelLvl1.cpp:19-144 with the measured
+  // Daxpy / Ddot tile tables and the shared host-link model): a vector that already sits on
+  // a GPU ends up processed there, host vectors are spread over as many GPUs as the host
+  // links reward; the caller's control values override either choice.
   const double t_plan0 = wall_ms();
-  std::vector<int> devs;
-  if (ctl && ctl->active_unit_num > 0) {
-    for (int i = 0; i < ctl->active_unit_num && i < PARALIA_MAX_UNITS; ++i) {
-      const int d = ctl->active_unit_id_list[i];
-      if (d < 0 || d >= ngpu) { cleanup(); return fail(PARALIA_ERR_INVALID_ARG, "unit id %d is not a GPU", d); }
-      devs.push_back(d);
-    }
-  } else if (vy.loc >= 0) devs.push_back(vy.loc);
-  else if (vx.loc >= 0) devs.push_back(vx.loc);
-  else for (int d = 0; d < ngpu; ++d) devs.push_back(d);
+  VecModelInput vin;
+  vin.func = is_dot ? "Ddot" : "Daxpy";
+  vin.N = N;
+  vin.locx = vx.loc;
+  vin.locy = vy.loc;
+  paralia_report tuned;
+  rc = autotune_vec(vin, ngpu, ctl, &tuned);
+  if (rc != PARALIA_OK) { cleanup(); return rc; }
+  std::vector<int> devs(tuned.active_unit_id_list, tuned.active_unit_id_list + tuned.active_unit_num);
   int U = (int)devs.size();
-
-  int64_t T = (ctl && ctl->T > 0) ? ctl->T : 0;
-  if (T <= 0) {
-    // At least eight tiles per GPU so that copy-in, kernel and copy-out overlap; tiles
-    // between 2^16 and 2^25 elements (0.5 MiB .. 256 MiB).
-    T = ceil_div(N, (int64_t)U * 8);
-    T = std::min<int64_t>(std::max<int64_t>(T, 1 << 16), 1 << 25);
-    T = ceil_div(T, 1024) * 1024;
-  }
+  int64_t T = tuned.T;
+  rep->pred_t = tuned.pred_t;
   if (T > N) T = N;
   const int64_t Nt = ceil_div(N, T);
   if (Nt < U) U = (int)Nt;

@@ -1,6 +1,8 @@
 #include <algorithm>
 #include "runtime.hpp"
 
+#include <dlfcn.h>
+
 #include <chrono>
 #include <cstdarg>
 #include <cstdio>
@@ -51,9 +53,25 @@ int Runtime::init() {
   for (int d = 0; d < n; ++d) devs_[d].dev = d;
   inited_ = true;
   // Calibration database named by the environment (reference: compile-time DEPLOYDB).
+  // Otherwise the tables shipped beside the library (<dir of libparalia.so>/../db_b200).
   if (const char* db = getenv("PARALIA_DB")) {
     reset_database_defaults(ndev_);
     if (load_database(db) != PARALIA_OK) fprintf(stderr, "libparalia: %s\n", last_error_cstr());
+  } else {
+    Dl_info info;
+    if (dladdr(reinterpret_cast<const void*>(&wall_ms), &info) && info.dli_fname) {
+      std::string path(info.dli_fname);
+      const size_t cut = path.rfind('/');
+      if (cut != std::string::npos) {
+        const std::string db = path.substr(0, cut) + "/../db_b200";
+        FILE* probe = fopen((db + "/Processed/Dgemm_lookup-table_dev-0.log").c_str(), "r");
+        if (probe) {
+          fclose(probe);
+          reset_database_defaults(ndev_);
+          if (load_database(db.c_str()) != PARALIA_OK) reset_database_defaults(ndev_);
+        }
+      }
+    }
   }
   return PARALIA_OK;
 }
@@ -125,6 +143,9 @@ int Runtime::ensure_device(int d) {
     PL_CUDA(cudaEventCreateWithFlags(&c.stage_free[i], cudaEventDisableTiming));
   PL_CUDA(cudaEventCreate(&c.t_begin));
   PL_CUDA(cudaEventCreate(&c.t_end));
+  PL_CUDA(cudaEventCreate(&c.t_first_exec));
+  PL_CUDA(cudaEventCreate(&c.t_h2d_end));
+  for (int i = 0; i < MAX_EXEC_STREAMS; ++i) PL_CUDA(cudaEventCreate(&c.t_exec_end[i]));
   PL_CUDA(cudaEventCreateWithFlags(&c.caller_ready, cudaEventDisableTiming));
   PL_CUDA(cudaMalloc(&c.status_dev, sizeof(int)));
   PL_CUDA(cudaMemset(c.status_dev, 0, sizeof(int)));
@@ -290,6 +311,10 @@ int Runtime::finalize() {
       cudaEventDestroy(c.t_begin);
       if (c.caller_ready) cudaEventDestroy(c.caller_ready);
       cudaEventDestroy(c.t_end);
+      if (c.t_first_exec) cudaEventDestroy(c.t_first_exec);
+      if (c.t_h2d_end) cudaEventDestroy(c.t_h2d_end);
+      for (int i = 0; i < MAX_EXEC_STREAMS; ++i)
+        if (c.t_exec_end[i]) cudaEventDestroy(c.t_exec_end[i]);
     }
   }
   devs_.clear();

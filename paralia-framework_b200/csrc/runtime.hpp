@@ -53,6 +53,10 @@ struct DeviceCtx {
   bool stage_used[STAGE_SLOTS] = {};
   int stage_next = 0;
   cudaEvent_t t_begin = nullptr, t_end = nullptr;  // timing events
+  // Phases of a call: start of the first kernel, end of the last kernel per compute stream,
+  // end of the host -> GPU stream.
+  cudaEvent_t t_first_exec = nullptr, t_h2d_end = nullptr;
+  cudaEvent_t t_exec_end[MAX_EXEC_STREAMS] = {};
   cudaEvent_t caller_ready = nullptr;  // marks the caller's default-stream work at call entry
   // Tile cache: one allocation cut into equal blocks (reference: Buffer / CBlock,
   // sized by ManageCachesDgemm, Library_scheduler/src/Functions/dgemm.cpp:23-121).

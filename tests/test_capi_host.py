@@ -84,17 +84,114 @@ def test_autotune_fixed_units_no_gpu(pl, orc):
     # the model alone, with a caller-fixed unit list: no GPU is touched
     ctl = pl.make_ctl(units=list(range(8)))
     rep = pl.autotune_gemm(8, "N", "N", 32768, 32768, 32768, -1, -1, -1, ctl)
-    want_T, want_sl = orc.optimize_tile(32768, 32768, 32768, 8, step=128)
-    assert rep.T == want_T == 2048
-    assert list(rep.T_slowdowns) == want_sl
+    assert rep.T in (2048, 4096)
+    # the reference's tile score of the chosen tile is still reported (Autotuner.cpp:571-603)
+    assert list(rep.T_slowdowns) == orc.tile_slowdowns(32768, 32768, 32768, rep.T, 8)
     assert rep.active_unit_num == 8 and (rep.grid_d1, rep.grid_d2) == (2, 4)
-    assert rep.subkernel_num == 16 * 16 * 16
-    assert list(rep.subkernels_per_unit[:8]) == [512] * 8
+    nt = 32768 // rep.T
+    assert rep.subkernel_num == nt ** 3
+    assert list(rep.subkernels_per_unit[:8]) == [nt ** 3 // 8] * 8
     assert rep.pred_t > 0
     # a caller-fixed T is kept
     rep = pl.autotune_gemm(8, "N", "N", 32768, 32768, 32768, -1, -1, -1,
                            pl.make_ctl(T=4096, units=[0, 1]))
     assert rep.T == 4096 and rep.active_unit_num == 2
+
+
+@pytest.mark.parametrize("esz,dims,locs,units", [
+    (8, (32768, 32768, 32768), (-1, -1, -1), 1), (8, (32768, 32768, 32768), (-1, -1, -1), 8),
+    (8, (32768, 32768, 32768), (-1, -1, -1), 4), (8, (4096, 4096, 4096), (-1, -1, -1), 1),
+    (8, (65536, 65536, 2048), (0, 1, -1), 2), (4, (40960, 40960, 40960), (-1, -1, -1), 8),
+    (8, (8192, 8192, 8192), (0, 0, 0), 1), (8, (1156, 1412, 1228), (-1, -1, -1), 3),
+])
+def test_tile_is_the_argmin_of_the_predicted_time(pl, esz, dims, locs, units):
+    # the tile edge is chosen by the model: no forced tile size predicts a shorter time
+    M, N, K = dims
+    us = list(range(units))
+    chosen = pl.autotune_gemm(esz, "N", "N", M, N, K, *locs, pl.make_ctl(units=us))
+    assert chosen.T % 16 == 0 or chosen.T == min(dims)
+    for T in (256, 512, 1024, 2048, 3072, 4096, 5120, 8192):
+        if T > min(dims):
+            continue
+        forced = pl.autotune_gemm(esz, "N", "N", M, N, K, *locs, pl.make_ctl(T=T, units=us))
+        assert chosen.pred_t <= forced.pred_t * (1 + 1e-9), (T, chosen.T, chosen.pred_t, forced.pred_t)
+
+
+def test_beta_zero_flag_drops_the_fetch_of_c(pl):
+    # write-back-bound shape of BASELINE configs[2]: with beta == 0 C crosses the host link once
+    args = (8, "T", "N", 65536, 65536, 2048, 0, 1, -1)
+    with_c = pl.autotune_gemm(*args, pl.make_ctl(T=2048, units=[0, 1]))
+    without = pl.autotune_gemm(*args, pl.make_ctl(T=2048, units=[0, 1], flags=pl.FLAG_BETA_ZERO))
+    assert without.pred_t < 0.75 * with_c.pred_t
+
+
+def _write_db(tmp_path, links, aggregate=None):
+    proc = tmp_path / "Processed"
+    proc.mkdir(parents=True, exist_ok=True)
+    for (dst, src), (ti, tb, slow) in links.items():
+        text = f"Intercept: {ti:e}\nCoefficient: {tb:e}\n"
+        text += "".join(f"Slowdown([{s}]->[{d}]): {r:e}\n" for (d, s, r) in slow)
+        (proc / f"Link-Stats_loc_dest-{dst}_loc_src-{src}.log").write_text(text)
+    if aggregate is not None:
+        (proc / "Host-Link-Aggregate.log").write_text(
+            "".join(f"{k} {n} {v:e}\n" for (k, n, v) in aggregate))
+    return str(tmp_path)
+
+
+def test_shared_host_link_model(pl, tmp_path):
+    # reference: Slowdown lines CoModel.cpp:32-55, shared prediction CoModel.cpp:120-140
+    tb = 1.0 / 50e9
+    links = {
+        (0, -1): (0.0, tb, [(1, -1, 1.6), (-1, 0, 1.25), (2, -1, 1.02), (3, -1, 3.0)]),
+        (1, -1): (0.0, tb, []), (2, -1): (0.0, tb, []), (3, -1): (0.0, tb, []),
+        (-1, 0): (0.0, tb, []),
+    }
+    agg = [("H2D", 1, 50.0), ("H2D", 2, 100.0), ("H2D", 4, 120.0), ("D2H", 1, 50.0), ("D2H", 4, 120.0),
+           ("BIDIR", 1, 45.0), ("BIDIR", 2, 90.0), ("BIDIR", 4, 50.0)]
+    try:
+        pl.load_database(_write_db(tmp_path, links, agg))
+        gb = 10 ** 9
+        alone, _ = pl.model_host_link(0, True, gb, 1)
+        assert alone == pytest.approx(1 / 50.0)
+        # a busy partner link slows this one by its measured ratio
+        t, _ = pl.model_host_link(0, True, gb, 2, active_devs=[0, 1])
+        assert t == pytest.approx(1.6 / 50.0)
+        # ratios within 5 % of 1 are dropped; ratios above 2 are clamped to 2
+        t, _ = pl.model_host_link(0, True, gb, 2, active_devs=[0, 2])
+        assert t == pytest.approx(1 / 50.0)
+        t, _ = pl.model_host_link(0, True, gb, 2, active_devs=[0, 3])
+        assert t == pytest.approx(2.0 / 50.0)
+        # the opposite direction of the same GPU counts only when it is busy
+        t, _ = pl.model_host_link(0, True, gb, 1, both_directions=True, active_devs=[0])
+        assert t == pytest.approx(max(1.25 / 50.0, 1 / 45.0))
+        # the aggregate caps what four GPUs get together: 120 / 4 = 30 GB/s each
+        t, defer4 = pl.model_host_link(2, True, gb, 4, active_devs=[0, 1, 2, 3])
+        assert t == pytest.approx(1 / 30.0)
+        # three GPUs: between the measured points 2 -> 100 and 4 -> 120
+        t, _ = pl.model_host_link(2, True, gb, 3, active_devs=[1, 2, 3])
+        assert t == pytest.approx(3 / 110.0)
+        # write-backs are deferred where both directions together deliver less than one
+        # after the other: 2 x 50 < 0.92 x 120 at four GPUs, 2 x 90 > 100 at two
+        _, defer2 = pl.model_host_link(0, True, gb, 2)
+        assert defer4 is True and defer2 is False
+    finally:
+        pl.load_database(str(pl.DEFAULT_DB))
+
+
+def test_level1_model_picks_units_and_tile(pl):
+    n = 1 << 30
+    # host-resident vectors: every GPU brings its own host link, so all of them are used
+    rep = pl.autotune_vec(False, n, -1, -1, pl.make_ctl(units=list(range(8))))
+    assert rep.active_unit_num == 8 and (1 << 16) <= rep.T <= (1 << 25) and rep.pred_t > 0
+    one = pl.autotune_vec(False, n, -1, -1, pl.make_ctl(units=[0]))
+    assert rep.pred_t < one.pred_t
+    # a caller-fixed tile length is kept; DDOT moves less than DAXPY
+    dot = pl.autotune_vec(True, n, -1, -1, pl.make_ctl(T=1 << 22, units=[0]))
+    axpy = pl.autotune_vec(False, n, -1, -1, pl.make_ctl(T=1 << 22, units=[0]))
+    assert dot.T == 1 << 22 and dot.pred_t < axpy.pred_t
+    # device-resident: HBM-bound, about 24 B x 2^30 / 6.3 TB/s
+    dev = pl.autotune_vec(False, n, 0, 0, pl.make_ctl(units=[0]))
+    assert 0.003 < dev.pred_t < 0.006
 
 
 def test_autotune_more_units_predicts_faster(pl):
@@ -141,17 +238,25 @@ def test_database_round_trip(pl, tmp_path):
         for (d, s) in ((g, -1), (-1, g)):
             (proc / f"Link-Stats_loc_dest-{d}_loc_src-{s}.log").write_text(
                 "Intercept: 1.000000e-05\nCoefficient: 2.000000e-11\nSlowdown([0]->[1]): 1.000000e+00\n")
+    # no aggregate cap in this database: the link files alone decide
+    (proc / "Host-Link-Aggregate.log").write_text(
+        "".join(f"{k} {n} 1.0e+06\n" for k in ("H2D", "D2H", "BIDIR") for n in (1, 8)))
     pl.load_database(str(tmp_path))
     try:
         rep = pl.autotune_gemm(8, "N", "N", 32768, 32768, 32768, -1, -1, -1,
                                pl.make_ctl(units=list(range(8))))
-        assert rep.T == 2048
-        t_exec = (32768 / 2048) ** 3 * (2.0 * 2048 ** 3 / rate) / 8
-        t_recv = 3 * (1e-5 + 2e-11 * 32768 * 32768 * 8 / 8)
+        # the same rate at every tile size: the smallest tile wins (least fill and drain)
+        assert rep.T == 1024 and (rep.grid_d1, rep.grid_d2) == (2, 4)
+        tile = 1024 * 1024 * 8
+        t_exec = (16384 / 1024) * (8192 / 1024) * 32 * (2.0 * 1024 ** 3 / rate)
+        # per GPU: a quarter of its A row panel, half of its B column panel, its C block
+        t_recv = 1e-5 + 2e-11 * 3 * 2 ** 30
         assert t_exec > t_recv
-        # what overlap cannot hide: first A, B and C tiles in, last C tile out (4 tile copies)
-        t_fill = 4 * (1e-5 + 2e-11 * 2048 * 2048 * 8)
-        assert rep.pred_t == pytest.approx(t_exec * (1 + rep.T_slowdowns[0]) + t_fill, rel=1e-5)
+        # what overlap cannot hide: the first host tile in (A and B come over different host
+        # links on a 2 x 4 grid) and its GPU -> GPU forward, the last band's two C tiles out
+        t_fill = (1e-5 + 2e-11 * tile) + (10e-6 + tile / 700e9)
+        t_drain = 1e-5 + 2e-11 * 2 * tile
+        assert rep.pred_t == pytest.approx(t_fill + t_exec + t_drain, rel=1e-6)
         # a slow host link makes the same problem link-bound
         for g in range(8):
             (proc / f"Link-Stats_loc_dest-{g}_loc_src--1.log").write_text(
@@ -159,10 +264,10 @@ def test_database_round_trip(pl, tmp_path):
         pl.load_database(str(tmp_path))
         rep2 = pl.autotune_gemm(8, "N", "N", 32768, 32768, 32768, -1, -1, -1,
                                 pl.make_ctl(units=list(range(8))))
-        t_recv2 = 3 * (1e-5 + 1e-9 * 32768 * 32768 * 8 / 8)
-        tile = rep2.T * rep2.T * 8     # three tiles in over the slow direction, one out over the fast
-        t_fill2 = 3 * (1e-5 + 1e-9 * tile) + (1e-5 + 2e-11 * tile)
-        assert rep2.pred_t == pytest.approx(t_recv2 * (1 + rep2.T_slowdowns[0]) + t_fill2, rel=1e-5)
+        assert rep2.T == 1024
+        t_recv2 = 1e-5 + 1e-9 * 3 * 2 ** 30
+        t_fill2 = (1e-5 + 1e-9 * tile) + (10e-6 + tile / 700e9)
+        assert rep2.pred_t == pytest.approx(t_recv2 + t_fill2, rel=1e-6)
     finally:
         with pytest.raises(pl.ParaliaError):
             pl.load_database(str(tmp_path / "nowhere"))   # DB missing -> status, state kept
@@ -230,14 +335,14 @@ def test_predictor_mode_needs_no_gpu_with_a_unit_list(pl, capsys):
     out = runner.main(["dgemm_predict", "8", "11111111", "-1", "-1", "N", "N", "1", "1",
                        "32768", "32768", "32768", "-1", "-1", "-1", "-1"])
     capsys.readouterr()
-    assert out["T"] == 2048 and out["grid"] == [2, 4] and out["units"] == list(range(8))
-    assert out["subkernels"] == 16 ** 3
+    assert out["T"] in (2048, 4096) and out["grid"] == [2, 4] and out["units"] == list(range(8))
+    assert out["subkernels"] == (32768 // out["T"]) ** 3
     # host-resident 32768^3 on 8 B200: the model says compute-bound, 0.25-0.30 s
     assert 0.25 < out["pred_t"] < 0.30
     one = runner.main(["dgemm_predict", "1", "1", "-1", "-1", "N", "N", "1", "1",
                        "32768", "32768", "32768", "-1", "-1", "-1", "-1"])
     capsys.readouterr()
-    assert one["T"] == 4096 and 1.9 < one["pred_t"] < 2.2
+    assert one["T"] in (4096, 8192) and 1.9 < one["pred_t"] < 2.2
 
 
 @pytest.mark.parametrize("dims,T,units", [((32768, 32768, 32768), 2048, 8), ((32768, 32768, 32768), 4096, 1),
@@ -283,3 +388,40 @@ def test_launch_plan_is_complete_and_static(pl, dims, T, units, bounded):
             mine = [(mi, ni) for (uu, mi, ni, _a, _b) in items if uu == u]
             order = [t for i, t in enumerate(mine) if i == 0 or mine[i - 1] != t]
             assert len(order) == len(set(order))
+
+
+def _bands_of_unit(items, unit):
+    """Band sizes of one unit read off its launch order: a band is a run of first-k launches."""
+    bands, run = [], 0
+    for (u, _mi, _ni, k0, _k1) in items:
+        if u != unit:
+            continue
+        if k0 == 0:
+            run += 1
+        elif run:
+            bands.append(run)
+            run = 0
+    if run:
+        bands.append(run)
+    return bands
+
+
+@pytest.mark.parametrize("T,units", [(2048, 8), (4096, 8), (4096, 4), (4096, 1), (8192, 1)])
+def test_band_sizes_first_band_feeds_itself_and_the_tail_shrinks(pl, T, units):
+    pl.load_database(str(pl.DEFAULT_DB))
+    n = 32768
+    items, (d1, d2) = pl.plan_gemm(n, n, n, T, units)
+    per_unit = (n // T) ** 2 // units
+    for u in range(units):
+        bands = _bands_of_unit(items, u)
+        assert sum(bands) == per_unit
+        # what is left to write back after the last launch is one or two tiles
+        assert bands[-1] <= 2
+        if len(bands) > 1:
+            assert bands[-1] <= bands[-2]
+        # whole tile rows of the unit's block in the first band
+        row = (n // T) // d2
+        assert bands[0] % row == 0 or bands[0] == per_unit
+    if (T, units) == (2048, 8):
+        # eight GPUs share 185 GB/s of host link: two tile rows (8 tiles) would be input-bound
+        assert _bands_of_unit(items, 0)[0] >= 12
