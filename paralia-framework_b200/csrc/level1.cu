@@ -238,6 +238,14 @@ std::mutex g_noalloc_mutex;
 double* g_noalloc_ptr[PARALIA_MAX_UNITS] = {};
 
 }  // namespace
+
+// Forget the looked-up addresses (library shutdown: after a device reset the next call must
+// ask the runtime again instead of using an address of a context that is gone).
+void ddot_noalloc_forget_addresses() {
+  std::lock_guard<std::mutex> lk(g_noalloc_mutex);
+  for (double*& p : g_noalloc_ptr) p = nullptr;
+}
+
 }  // namespace paralia
 
 extern "C" int64_t PARALiA_tile_ddot_noalloc_max_n(void) { return (int64_t)1 << 31; }

@@ -18,6 +18,9 @@ cudaError_t launch_ddot(int64_t n, const double* x, int64_t incx, const double* 
                         double* partials, double* result_dev, cudaStream_t stream,
                         int* launches);
 
+// Drops the cached device addresses of the allocation-free dot product's static scratch.
+void ddot_noalloc_forget_addresses();
+
 cudaError_t launch_fill_f64(double* p, int64_t n, uint64_t seed, int dist, cudaStream_t stream);
 cudaError_t launch_fill_f32(float* p, int64_t n, uint64_t seed, int dist, cudaStream_t stream);
 

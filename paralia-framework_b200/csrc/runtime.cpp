@@ -11,6 +11,7 @@
 
 #include "autotune.hpp"
 #include "dgemm_tile.cuh"
+#include "level1.cuh"
 #include "sgemm_tile.cuh"
 
 namespace paralia {
@@ -317,6 +318,7 @@ int Runtime::finalize() {
         if (c.t_exec_end[i]) cudaEventDestroy(c.t_exec_end[i]);
     }
   }
+  ddot_noalloc_forget_addresses();
   devs_.clear();
   ndev_ = 0;
   inited_ = false;

@@ -17,6 +17,10 @@ parse them unchanged::
     <db>/Benchmark-Results/CuCuBLAS_link_overlap_benchmark_loc_dest-<d>_loc_src-<s>_<ver>.log  other_dest,other_src, t_alone,t_shared,10, bench_t
     <db>/Processed/<Func>_lookup-table_dev-<d>.log     TransA,TransB,T,T,T,mean_t,W,J,err,samples,bench_t
     <db>/Processed/Link-Stats_loc_dest-<d>_loc_src-<s>.log   Intercept / Coefficient / Slowdown([s']->[d']) lines
+    <db>/Benchmark-Results/cublasDaxpy_dev-<d>_<ver>.log, cublasDdot_...   N, mean_t,W,J,err,samples,bench_t
+    <db>/Processed/Daxpy_lookup-table_dev-<d>.log, Ddot_...    N,mean_t,W,J,err,samples,bench_t
+    <db>/Processed/Host-Link-Aggregate.log    "H2D|D2H|BIDIR <gpus> <aggregate GB/s per direction>"
+                                              (no counterpart in the reference)
 
 Energy columns (W, J) are written as 0: power measurement is not built.
 
@@ -91,8 +95,10 @@ def build_exec(pl, db: Path, dev: int, quick: bool):
         for tb in "NT":
             lines = []
             for T in tile_sizes(quick):
+                # the time of one k tile inside the launches the executor issues: chains of
+                # four k tiles per C tile, eight launches over four streams
                 mean, err, n, bt = sample_until_confident(
-                    lambda: pl.bench_tile_dgemm(dev, ta, tb, T, 8))   # 8 tiles over 4 streams: in-pipeline time
+                    lambda: pl.bench_tile_dgemm_chain(dev, ta, tb, T, 4, 8))
                 lines.append(f"{T},{T},{T}, {mean:e},0,0,{err:e},{n},{bt:e}")
                 rows["Dgemm"].append((ta, tb, T, mean, err, n, bt))
             (raw / f"cublasDgemm_dev-{dev}_TransA-{ta}_TransB-{tb}_{VERSION}.log").write_text(
@@ -114,6 +120,44 @@ def build_exec(pl, db: Path, dev: int, quick: bool):
         text = "".join(f"{ta},{tb},{T},{T},{T},{m:e},0.000000e+00,0.000000e+00,{e:e},{n},{bt:e}\n"
                        for (ta, tb, T, m, e, n, bt) in rs)
         (db / "Processed" / f"{func}_lookup-table_dev-{dev}.log").write_text(text)
+
+
+def vector_lengths(quick: bool):
+    if quick:
+        return [1 << 16, 1 << 18, 1 << 20, 1 << 22, 1 << 24]
+    # the reference starts at 4096 with a step of 4096 that doubles every 16 steps
+    # (daxpy_microbench.cu:109-111); tiles the executor uses lie between 2^16 and 2^25
+    out, n, step = [], 1 << 16, 1 << 16
+    while n <= (1 << 25):
+        out.append(n)
+        if n >= step * 16:
+            step *= 2
+        n += step
+    return out
+
+
+def build_level1(pl, db: Path, dev: int, quick: bool):
+    """Daxpy / Ddot tile tables (daxpy_microbench.cu:26-231, ddot_microbench.cu:26-228)."""
+    raw = db / "Benchmark-Results"
+    for func, fn in (("Daxpy", pl.bench_tile_daxpy), ("Ddot", pl.bench_tile_ddot)):
+        raw_lines, rows = [], []
+        for n in vector_lengths(quick):
+            mean, err, cnt, bt = sample_until_confident(lambda: fn(dev, n, 8), budget_s=0.5)
+            raw_lines.append(f"{n}, {mean:e},0,0,{err:e},{cnt},{bt:e}")
+            rows.append(f"{n},{mean:e},0.000000e+00,0.000000e+00,{err:e},{cnt},{bt:e}")
+        (raw / f"cublas{func}_dev-{dev}_{VERSION}.log").write_text("\n".join(raw_lines) + "\n")
+        (db / "Processed" / f"{func}_lookup-table_dev-{dev}.log").write_text("\n".join(rows) + "\n")
+
+
+def build_host_aggregate(pl, db: Path, ngpu: int, quick: bool):
+    """Aggregate host-link bandwidth against the number of GPUs copying at once."""
+    counts = sorted({c for c in (1, 2, 4, 8, ngpu) if c <= ngpu})
+    nbytes = (128 if quick else 512) << 20
+    lines = []
+    for mode, tag in ((0, "H2D"), (1, "D2H"), (2, "BIDIR")):
+        for c in counts:
+            lines.append(f"{tag} {c} {pl.bench_host_aggregate(c, mode, nbytes, 3):e}")
+    (db / "Processed" / "Host-Link-Aggregate.log").write_text("\n".join(lines) + "\n")
 
 
 def linear_fit(xs, ys):
@@ -149,6 +193,10 @@ def build_links(pl, db: Path, locs: list[int], quick: bool):
                 for os_ in locs:
                     if od == os_ or (od == d and os_ == s) or (od == -1 and os_ == -1):
                         continue
+                    # behind NVSwitch every GPU pair has its own path: only host links can
+                    # contend, so only pairs of host links are probed
+                    if not ((d == -1 or s == -1) and (od == -1 or os_ == -1)):
+                        continue
                     t0 = time.perf_counter()
                     ta_, ts_ = pl.bench_link_overlap(d, s, od, os_, 2048 if quick else 4096, 3)
                     olines.append(f"{od},{os_}, {ta_:e},{ts_:e},10, {time.perf_counter() - t0:e}")
@@ -165,6 +213,9 @@ def main(argv=None):
     ap.add_argument("db")
     ap.add_argument("--gpus", type=int, default=0, help="GPUs to calibrate links for (0 = all)")
     ap.add_argument("--quick", action="store_true")
+    ap.add_argument("--links-only", action="store_true",
+                    help="measure only the links and the host aggregate (the tile tables of "
+                         "one GPU serve every identical GPU)")
     a = ap.parse_args(argv)
     pl = _pkg()
     pl.init()
@@ -172,8 +223,11 @@ def main(argv=None):
     (db / "Benchmark-Results").mkdir(parents=True, exist_ok=True)
     (db / "Processed").mkdir(parents=True, exist_ok=True)
     ngpu = pl.device_count() if a.gpus <= 0 else min(a.gpus, pl.device_count())
-    build_exec(pl, db, 0, a.quick)      # identical GPUs: device 0's curve serves all
+    if not a.links_only:
+        build_exec(pl, db, 0, a.quick)      # identical GPUs: device 0's curve serves all
+        build_level1(pl, db, 0, a.quick)
     build_links(pl, db, [-1] + list(range(ngpu)), a.quick)
+    build_host_aggregate(pl, db, ngpu, a.quick)
     peak = max(pl.bench_dmma_peak(0, s, 20000) for s in (884, 1688, 16816))
     (db / "Processed" / "fp64_tensor_peak_dev-0.log").write_text(f"{peak:e}\n")
     print(f"database written to {db} ({ngpu} GPU(s))")

@@ -188,3 +188,103 @@ def test_config5_daxpy_ddot_2_30(pl):
     assert torch.equal(y, want)
     del x, y, want
     _release(pl)
+
+
+def _host_ok(gib):
+    import psutil
+    if psutil.virtual_memory().available < gib * GiB:
+        pytest.skip(f"needs {gib} GiB of free host memory")
+
+
+def _pinned_from_device(pl, dev_tensor, nbytes, dev):
+    """A pinned host copy of a device buffer (raw pointer, freed by the caller)."""
+    h = pl.malloc(nbytes, -1)
+    pl.memcpy(h, -1, dev_tensor, dev, nbytes)
+    return h
+
+
+def test_config2_dgemm_32768_host_resident_all_gpus_freivalds(pl):
+    """DGEMM NN 32768^3, alpha = beta = 1, A, B and C in pinned host memory as the
+    configuration states, on every GPU of the box through the in-process scheduler."""
+    import torch
+    _need(60)
+    _host_ok(40)
+    n = 32768
+    g = torch.cuda.device_count()
+    dev = "cuda:0"
+    A = torch.empty((n, n), dtype=torch.float64, device=dev)
+    B = torch.empty((n, n), dtype=torch.float64, device=dev)
+    C0 = torch.empty((n, n), dtype=torch.float64, device=dev)
+    for t, seed in ((A, 42), (B, 43), (C0, 44)):
+        pl.fill_f64(t, n * n, seed, 0, 0)
+    nb = n * n * 8
+    hA, hB, hC = (_pinned_from_device(pl, t, nb, 0) for t in (A, B, C0))
+    try:
+        ctl = pl.make_ctl(units=list(range(g)))
+        rep = pl.dgemm("N", "N", n, n, n, 1.0, hA, n, hB, n, 1.0, hC, n, locA=-1, locB=-1, locC=-1, ctl=ctl)
+        assert rep.active_unit_num == g
+        # every host byte crosses the host link once: A, B, C in; C out
+        assert rep.h2d_bytes == 3 * nb and rep.d2h_bytes == nb
+        _release(pl)
+        C = torch.empty((n, n), dtype=torch.float64, device=dev)
+        pl.memcpy(C, 0, hC, -1, nb)
+        for x in _vectors(n, 0, torch.float64):
+            want = torch.mv(A.T, torch.mv(B.T, x)) + torch.mv(C0.T, x)
+            assert _rel(torch.mv(C.T, x), want) <= 8 * n * EPS64
+            assert _rel(torch.mv(C.T, x), want) <= 1e-13
+            want_t = torch.mv(B, torch.mv(A, x)) + torch.mv(C0, x)
+            assert _rel(torch.mv(C, x), want_t) <= 1e-13
+        # fixed tile order: a second call from the same inputs gives the same bits
+        pl.memcpy(hC, -1, C0, 0, nb)
+        pl.dgemm("N", "N", n, n, n, 1.0, hA, n, hB, n, 1.0, hC, n, locA=-1, locB=-1, locC=-1, ctl=ctl)
+        C2 = torch.empty((n, n), dtype=torch.float64, device=dev)
+        _release(pl)
+        pl.memcpy(C2, 0, hC, -1, nb)
+        assert torch.equal(C, C2)
+        del C, C2
+    finally:
+        for h in (hA, hB, hC):
+            pl.free(h, -1)
+        del A, B, C0
+        _release(pl)
+
+
+def test_config4_sgemm_40960_host_resident_all_gpus_freivalds(pl):
+    """SGEMM NN 40960^3, alpha = 1, beta = 0, normal(0,1), operands in pinned host memory, on
+    every GPU of the box."""
+    import torch
+    _need(60)
+    _host_ok(30)
+    n = 40960
+    g = torch.cuda.device_count()
+    dev = "cuda:0"
+    A = torch.empty((n, n), dtype=torch.float32, device=dev)
+    B = torch.empty((n, n), dtype=torch.float32, device=dev)
+    pl.fill_f32(A, n * n, 42, 1, 0)
+    pl.fill_f32(B, n * n, 43, 1, 0)
+    nb = n * n * 4
+    hA, hB = _pinned_from_device(pl, A, nb, 0), _pinned_from_device(pl, B, nb, 0)
+    hC = pl.malloc(nb, -1)
+    try:
+        ctl = pl.make_ctl(units=list(range(g)))
+        rep = pl.sgemm("N", "N", n, n, n, 1.0, hA, n, hB, n, 0.0, hC, n, locA=-1, locB=-1, locC=-1, ctl=ctl)
+        assert rep.active_unit_num == g
+        assert rep.h2d_bytes == 2 * nb and rep.d2h_bytes == nb      # beta = 0: C is not fetched
+        _release(pl)
+        C = torch.empty((n, n), dtype=torch.float32, device=dev)
+        pl.memcpy(C, 0, hC, -1, nb)
+        prev = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = False
+        try:
+            for x in _vectors(n, 0, torch.float32):
+                want = torch.mv(A.T, torch.mv(B.T, x))
+                err = _rel(torch.mv(C.T, x), want)
+                assert err <= 4 * n * EPS32 and err <= 1e-3
+        finally:
+            torch.backends.cuda.matmul.allow_tf32 = prev
+        del C
+    finally:
+        for h in (hA, hB, hC):
+            pl.free(h, -1)
+        del A, B
+        _release(pl)
