@@ -38,7 +38,8 @@ enum {
   PARALIA_ERR_NO_PEER_ACCESS = 5,
   PARALIA_ERR_DB_MISSING = 6,
   PARALIA_ERR_NO_DEVICE = 7,
-  PARALIA_ERR_UNSUPPORTED = 8
+  PARALIA_ERR_UNSUPPORTED = 8,
+  PARALIA_ERR_GROUP_FAILED = 9   /* another rank of the process group failed or went missing */
 };
 
 /*
@@ -98,6 +99,24 @@ typedef struct paralia_report {
   double  exec_end_ms;       /* until the last tile kernel ends                 */
   double  h2d_end_ms;        /* until the last host -> GPU copy ends            */
 } paralia_report;
+
+/* ---- environment variables -------------------------------------------------------
+ * Read once, at first use. None of them is needed for normal operation.
+ *   PARALIA_DB               directory of the calibration database (lookup tables and link
+ *                            models, reference DEPLOYDB); default: the tables shipped beside
+ *                            the library.
+ *   PARALIA_KCHAIN=<n>       k tiles per launch (default: 1 for the first launch of a C tile,
+ *                            then 4). CHANGES RESULT BITS: the k split decides where partial
+ *                            sums are rounded; results are bit-reproducible only for a fixed
+ *                            value. For experiments.
+ *   PARALIA_BAND=<n>, PARALIA_BAND_PLAN=<a,b,...>  force the band sizes of the launch order.
+ *                            Launch order only: no result bit changes.
+ *   PARALIA_DEFER_WB=<0|1>   force write-backs to overlap with (0) or follow (1) the input
+ *                            stream of a GPU; default: decided from the database. Order only.
+ *   PARALIA_GROUP_TIMEOUT_MS hand-shake time-out of process groups (default 60000).
+ *   PARALIA_JOIN_TIMEOUT_MS  deadline of the host join of a whole-problem call (default: the
+ *                            larger of 120000 and fifty times the predicted duration).
+ */
 
 /* ---- library life cycle ---------------------------------------------------------- */
 /* Discover GPUs, enable peer access between every pair (reference: CoCoEnableLinks,
@@ -193,6 +212,23 @@ int PARALiA_group_sgemm(char TransA, char TransB, int64_t Mloc, int64_t Nloc, in
  * by itself and the error word reached the host -- the path every device-side wait of this
  * library takes instead of hanging the GPU. The CUDA context stays usable afterwards. */
 int PARALiA_selftest_bounded_wait(int dev, double budget_ms);
+
+/* Same idea for the host side of a whole-problem call: the call joins its GPUs by waiting
+ * for their end events with a deadline (PARALIA_JOIN_TIMEOUT_MS, default the larger of two
+ * minutes and fifty times the predicted duration). The self test queues a kernel that ends by
+ * itself after kernel_ms and joins with deadline_ms; with deadline_ms < kernel_ms it returns
+ * PARALIA_ERR_TIMEOUT. Nothing hangs and the context stays usable. */
+int PARALiA_selftest_join_deadline(int dev, double kernel_ms, double deadline_ms);
+/* The hand-shake layer of process groups alone, without CUDA: `rounds` barriers between
+ * `world` processes over the shared segment `name`. fail_mode 0: nobody fails. 1: rank
+ * fail_rank reports an error of its own at round fail_round (what a collective call does when
+ * its arguments are bad or an allocation fails): the others return PARALIA_ERR_GROUP_FAILED
+ * at once. 2: that rank silently stops arriving: the others time out after
+ * PARALIA_GROUP_TIMEOUT_MS (default 60000), the first to do so abandons the group and the
+ * rest follow at once. *waited_ms (may be NULL) = time spent in the failing barrier. */
+int PARALiA_selftest_group_rendezvous(const char* name, int rank, int world, int rounds,
+                                      int fail_rank, int fail_round, int fail_mode,
+                                      double* waited_ms);
 
 /* ---- per-tile kernels on device-resident data ---------------------------------------
  * What the reference reaches through backend_run_operation(params, "Dgemm"|"Sgemm"|
@@ -311,6 +347,12 @@ int PARALiA_load_database(const char* dir);
 /* Register-only FP64 tensor-core loop; returns sustained TFLOP/s of GPU `dev`.
  * shape: 884, 1684, 1688 or 16816 (mma.sync m/n/k). */
 int PARALiA_bench_dmma_peak(int dev, int shape, int iters, double* tflops);
+/* The issue loop of the FP32 kernel's tensor-core instruction (tcgen05.mma.kind::tf32,
+ * M = 128, N = 256, K = 8, operands resident in shared memory, no global traffic) on every SM
+ * of GPU `dev`: `stages` x 6 MMAs per SM. Returns the dense TF32 TFLOP/s sustained over the
+ * run; the 3xTF32 kernel's roofline is a third of it. A few thousand stages give the burst
+ * figure, a few hundred thousand (about a second) the figure under the power cap. */
+int PARALiA_bench_tf32_peak(int dev, int stages, double* tflops);
 /* Time `reps` launches of the tile DGEMM on square T; returns mean seconds. */
 int PARALiA_bench_tile_dgemm(int dev, char TransA, char TransB, int64_t T, int reps,
                              double* mean_s);

@@ -36,6 +36,7 @@ ERR_NO_PEER_ACCESS = 5
 ERR_DB_MISSING = 6
 ERR_NO_DEVICE = 7
 ERR_UNSUPPORTED = 8
+ERR_GROUP_FAILED = 9
 
 
 class LibraryMissing(RuntimeError):
@@ -166,6 +167,10 @@ SIGNATURES = {
     "PARALiA_bench_tile_dgemm_chain": (C.c_int, [C.c_int, _chr, _chr, _i64, C.c_int, C.c_int,
                                                  C.POINTER(_dbl)]),
     "PARALiA_bench_tile_sgemm": (C.c_int, [C.c_int, _i64, C.c_int, C.POINTER(_dbl)]),
+    "PARALiA_bench_tf32_peak": (C.c_int, [C.c_int, C.c_int, C.POINTER(_dbl)]),
+    "PARALiA_selftest_join_deadline": (C.c_int, [C.c_int, _dbl, _dbl]),
+    "PARALiA_selftest_group_rendezvous": (C.c_int, [C.c_char_p, C.c_int, C.c_int, C.c_int, C.c_int,
+                                                    C.c_int, C.c_int, C.POINTER(_dbl)]),
     "PARALiA_bench_tile_daxpy": (C.c_int, [C.c_int, _i64, C.c_int, C.POINTER(_dbl)]),
     "PARALiA_bench_tile_ddot": (C.c_int, [C.c_int, _i64, C.c_int, C.POINTER(_dbl)]),
     "PARALiA_bench_host_aggregate": (C.c_int, [C.c_int, C.c_int, _i64, C.c_int, C.POINTER(_dbl)]),
@@ -489,6 +494,25 @@ def bench_tile_dgemm_chain(dev, TransA, TransB, T, chain, reps) -> float:
     v = _dbl()
     _check(lib().PARALiA_bench_tile_dgemm_chain(dev, _c(TransA), _c(TransB), T, chain, reps, C.byref(v)))
     return v.value
+
+
+def bench_tf32_peak(dev, stages) -> float:
+    """Dense TF32 TFLOP/s of the tcgen05 instruction shape the FP32 kernel issues."""
+    v = _dbl()
+    _check(lib().PARALiA_bench_tf32_peak(dev, int(stages), C.byref(v)))
+    return v.value
+
+
+def selftest_join_deadline(dev, kernel_ms, deadline_ms) -> None:
+    _check(lib().PARALiA_selftest_join_deadline(dev, float(kernel_ms), float(deadline_ms)))
+
+
+def selftest_group_rendezvous(name, rank, world, rounds, fail_rank=-1, fail_round=0, fail_mode=0):
+    """Returns (status code, milliseconds spent in the failing barrier); never raises."""
+    w = _dbl()
+    rc = lib().PARALiA_selftest_group_rendezvous(name.encode(), rank, world, rounds, fail_rank,
+                                                 fail_round, fail_mode, C.byref(w))
+    return int(rc), w.value
 
 
 def bench_tile_daxpy(dev, N, reps) -> float:

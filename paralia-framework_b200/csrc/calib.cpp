@@ -14,6 +14,7 @@
 #include "autotune.hpp"
 #include "level1.cuh"
 #include "runtime.hpp"
+#include "sgemm_tile.cuh"
 
 namespace paralia {
 namespace {
@@ -83,6 +84,35 @@ int PARALiA_bench_tile_daxpy(int dev, int64_t N, int reps, double* mean_s) {
 
 int PARALiA_bench_tile_ddot(int dev, int64_t N, int reps, double* mean_s) {
   return bench_level1(true, dev, N, reps, mean_s);
+}
+
+int PARALiA_bench_tf32_peak(int dev, int stages, double* tflops) {
+  if (!tflops || stages <= 0) return fail(PARALIA_ERR_INVALID_ARG, "bad bench arguments");
+  Runtime& rt = Runtime::get();
+  PL_TRY(rt.init());
+  DeviceGuard guard;
+  PL_TRY(rt.ensure_device(dev));
+  PL_CUDA(cudaSetDevice(dev));
+  DeviceCtx& dc = rt.dev(dev);
+  int sms = 0;
+  PL_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  cudaEvent_t e0, e1;
+  PL_CUDA(cudaEventCreate(&e0));
+  PL_CUDA(cudaEventCreate(&e1));
+  cudaStream_t s = dc.exec[0];
+  cudaError_t e = launch_tf32_peak(std::min(stages, 2000), sms, dc.status_dev, s);   // warm-up
+  if (e == cudaSuccess) e = cudaEventRecord(e0, s);
+  if (e == cudaSuccess) e = launch_tf32_peak(stages, sms, dc.status_dev, s);
+  if (e == cudaSuccess) e = cudaEventRecord(e1, s);
+  if (e == cudaSuccess) e = cudaEventSynchronize(e1);
+  float ms = 0.f;
+  if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, e0, e1);
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  if (e != cudaSuccess) return fail(PARALIA_ERR_CUDA, "TF32 peak loop failed: %s", cudaGetErrorString(e));
+  PL_TRY(rt.check_status(dev));
+  *tflops = SG_PEAK_FLOP_PER_STAGE * (double)stages * sms / (ms * 1e-3) / 1e12;
+  return PARALIA_OK;
 }
 
 int PARALiA_bench_host_aggregate(int ngpu, int mode, int64_t bytes, int reps, double* gbs) {

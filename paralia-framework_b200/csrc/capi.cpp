@@ -4,6 +4,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <thread>
+#include <string>
 #include <vector>
 
 #include "autotune.hpp"
@@ -142,9 +143,9 @@ int PARALiA_tile_dgemm(int dev, void* stream, char TransA, char TransB, int64_t 
   }
   CUtensorMap mapA, mapB;
   PL_TRY(make_tensor_map(&mapA, A, 8, a_rows, a_cols, 1, ldA * 8, (uint64_t)ldA * a_cols * 8, 16,
-                         ta ? 128 : 16));
+                         ta ? DG_KC_BOX_ROWS : 16));
   PL_TRY(make_tensor_map(&mapB, B, 8, b_rows, b_cols, 1, ldB * 8, (uint64_t)ldB * b_cols * 8, 16,
-                         tb ? 16 : 128));
+                         tb ? 16 : DG_KC_BOX_ROWS));
   DgemmArgs args;
   memset(&args, 0, sizeof(args));
   args.C = C;
@@ -462,6 +463,38 @@ int PARALiA_selftest_bounded_wait(int dev, double budget_ms) {
   PL_CUDA(launch_bounded_wait_selftest(Runtime::get().dev(dev).status_dev, clocks, nullptr));
   PL_CUDA(cudaDeviceSynchronize());
   return Runtime::get().check_status(dev);
+}
+
+// The host join of the whole-problem routines waits for a GPU's end event with a deadline. A
+// kernel whose only wait runs out by itself after kernel_ms is queued and the join is given
+// deadline_ms < kernel_ms: it must come back with PARALIA_ERR_TIMEOUT instead of blocking.
+// The kernel then ends on its own, the status word is cleared and the context stays usable.
+int PARALiA_selftest_join_deadline(int dev, double kernel_ms, double deadline_ms) {
+  if (!(kernel_ms > 0.0) || kernel_ms > 1000.0 || !(deadline_ms > 0.0))
+    return fail(PARALIA_ERR_INVALID_ARG, "kernel_ms must be in (0, 1000], deadline_ms positive");
+  DeviceGuard guard;
+  PL_TRY(setup_device(dev));
+  DeviceCtx& dc = Runtime::get().dev(dev);
+  int khz = 0;
+  PL_CUDA(cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, dev));
+  const long long clocks = (long long)(kernel_ms * (double)khz);
+  PL_CUDA(launch_bounded_wait_selftest(dc.status_dev, clocks, dc.exec[0]));
+  PL_CUDA(cudaEventRecord(dc.t_end, dc.exec[0]));
+  const int rc = wait_event_with_deadline(dc.t_end, deadline_ms, dev);
+  std::string msg = rc != PARALIA_OK ? PARALiA_last_error() : "";
+  PL_CUDA(cudaStreamSynchronize(dc.exec[0]));   // the kernel gives up by itself
+  Runtime::get().check_status(dev);             // reads and clears the kernel's time-out word
+  if (rc != PARALIA_OK) return fail(rc, "%s", msg.c_str());
+  return PARALIA_OK;
+}
+
+int PARALiA_selftest_group_rendezvous(const char* name, int rank, int world, int rounds,
+                                      int fail_rank, int fail_round, int fail_mode,
+                                      double* waited_ms) {
+  if (rounds < 0 || fail_mode < 0 || fail_mode > 2)
+    return fail(PARALIA_ERR_INVALID_ARG, "bad self-test arguments");
+  return Group::selftest_rendezvous(name, rank, world, rounds, fail_mode ? fail_rank : -1, fail_round,
+                                    fail_mode, waited_ms);
 }
 
 int PARALiA_group_sgemm(char TransA, char TransB, int64_t Mloc, int64_t Nloc, int64_t K,

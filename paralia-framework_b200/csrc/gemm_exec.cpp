@@ -961,7 +961,7 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
       if (std::is_same<T, double>::value) {
         const uint64_t nb = dc.slab_bytes / g.block_bytes();
         rc = make_tensor_map(&u.map_slab_kc, dc.slab, g.esz, g.TL, g.TL, nb, g.TL * g.esz,
-                             g.block_bytes(), 16, 128);
+                             g.block_bytes(), 16, DG_KC_BOX_ROWS);
         if (rc == PARALIA_OK)
           rc = make_tensor_map(&u.map_slab_mn, dc.slab, g.esz, g.TL, g.TL, nb, g.TL * g.esz,
                                g.block_bytes(), 16, 16);
@@ -974,12 +974,12 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
     }
     if (u.a_native_ok && K > 0) {
       rc = make_tensor_map(&u.map_a_native, g.A.ptr, g.esz, g.A.rows, g.A.cols, 1, g.A.ld * g.esz,
-                           (uint64_t)g.A.ld * g.A.cols * g.esz, 16, g.A.trans ? 128 : 16);
+                           (uint64_t)g.A.ld * g.A.cols * g.esz, 16, g.A.trans ? DG_KC_BOX_ROWS : 16);
       if (rc != PARALIA_OK) return fail_out(rc);
     }
     if (u.b_native_ok && K > 0) {
       rc = make_tensor_map(&u.map_b_native, g.B.ptr, g.esz, g.B.rows, g.B.cols, 1, g.B.ld * g.esz,
-                           (uint64_t)g.B.ld * g.B.cols * g.esz, 16, g.B.trans ? 16 : 128);
+                           (uint64_t)g.B.ld * g.B.cols * g.esz, 16, g.B.trans ? 16 : DG_KC_BOX_ROWS);
       if (rc != PARALIA_OK) return fail_out(rc);
     }
   }
@@ -1094,10 +1094,10 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
     UnitState& u = g.units[ui];
     DeviceCtx& dc = rt.dev(u.dev);
     cudaSetDevice(u.dev);
-    cudaError_t e = cudaDeviceSynchronize();
-    if (e != cudaSuccess && rc == PARALIA_OK)
-      rc = fail(PARALIA_ERR_CUDA, "GPU %d failed while running the plan: %s", u.dev,
-                cudaGetErrorString(e));
+    // the end event of a unit follows everything the unit enqueued; the wait is bounded
+    // (a copy that never completes must not hang the caller)
+    if (rc == PARALIA_OK) rc = wait_event_with_deadline(dc.t_end, join_deadline_ms(rep->pred_t), u.dev);
+    else cudaDeviceSynchronize();
     if (rc == PARALIA_OK) {
       float ms = 0.f;
       if (cudaEventElapsedTime(&ms, dc.t_begin, dc.t_end) == cudaSuccess)
@@ -1125,6 +1125,23 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
   return rc;
 }
 
+// A collective call of one rank: whatever makes this rank leave the call early (a bad
+// argument, an allocation that fails, a CUDA error) is published to the group, so that the
+// peers -- which are inside, or about to enter, the call's hand-shakes -- return an error at
+// once instead of waiting out a time-out.
+template <typename Fn>
+int group_call(Group* grp, int64_t Mloc, int64_t Nloc, Fn&& run) {
+  if (grp->poisoned()) return grp->barrier();   // reports why the group was abandoned
+  int rc;
+  if (Mloc <= 0 || Nloc <= 0)
+    rc = fail(PARALIA_ERR_INVALID_ARG, "a rank's block of C is empty (%lld x %lld)", (long long)Mloc,
+              (long long)Nloc);
+  else
+    rc = run();
+  if (rc != PARALIA_OK && rc != PARALIA_ERR_GROUP_FAILED) grp->poison(last_error_cstr());
+  return rc;
+}
+
 }  // namespace
 
 int exec_dgemm(char ta, char tb, int64_t M, int64_t N, int64_t K, double alpha, const double* A,
@@ -1147,8 +1164,10 @@ int exec_group_dgemm(char ta, char tb, int64_t M, int64_t N, int64_t K, double a
                      const paralia_ctl* ctl, paralia_report* out) {
   Group* grp = Group::current();
   if (!grp) return fail(PARALIA_ERR_INVALID_ARG, "PARALiA_group_init has not been called");
-  return run_gemm<double>(ta, tb, M, N, K, alpha, A, ldA, locA, B, ldB, locB, beta, C, ldC, locC,
+  return group_call(grp, M, N, [&]() {
+    return run_gemm<double>(ta, tb, M, N, K, alpha, A, ldA, locA, B, ldB, locB, beta, C, ldC, locC,
                           ctl, out, "Dgemm", grp);
+  });
 }
 
 int exec_group_sgemm(char ta, char tb, int64_t M, int64_t N, int64_t K, float alpha, const float* A,
@@ -1156,8 +1175,10 @@ int exec_group_sgemm(char ta, char tb, int64_t M, int64_t N, int64_t K, float al
                      float* C, int64_t ldC, int locC, const paralia_ctl* ctl, paralia_report* out) {
   Group* grp = Group::current();
   if (!grp) return fail(PARALIA_ERR_INVALID_ARG, "PARALiA_group_init has not been called");
-  return run_gemm<float>(ta, tb, M, N, K, alpha, A, ldA, locA, B, ldB, locB, beta, C, ldC, locC,
-                         ctl, out, "Sgemm", grp);
+  return group_call(grp, M, N, [&]() {
+    return run_gemm<float>(ta, tb, M, N, K, alpha, A, ldA, locA, B, ldB, locB, beta, C, ldC, locC,
+                          ctl, out, "Sgemm", grp);
+  });
 }
 
 }  // namespace paralia

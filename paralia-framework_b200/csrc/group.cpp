@@ -37,6 +37,13 @@ struct Group::Shm {
   std::atomic<uint32_t> arrived;
   std::atomic<uint32_t> generation;
   std::atomic<uint32_t> attached;
+  // Set by the first rank that gives up on, or fails inside, a collective: from then on
+  // every hand-shake of every rank fails at once with the recorded reason, so that one
+  // rank's error never costs the others a time-out and an off-by-one arrival counter can
+  // never let a later barrier pass with a rank missing.
+  std::atomic<uint32_t> poisoned;
+  int32_t poison_rank;
+  char poison_msg[160];
   int32_t world;
   struct Rank {
     cudaIpcMemHandle_t slab_handle;
@@ -54,19 +61,15 @@ Group* Group::current() { return g_group; }
 
 const GroupCallInfo& Group::info(int peer) const { return shm_->ranks[peer].call; }
 
-int Group::init(const char* name, int rank, int world, int dev) {
-  if (g_group) return fail(PARALIA_ERR_INVALID_ARG, "a group is already initialised in this process");
+// Map the group's shared segment (rank 0 creates it) and wait until it is initialised.
+// No CUDA involved. On success *out is a Group with rank, world, grid and shm_ set.
+int Group::attach(const char* name, int rank, int world, Group** out) {
   if (!name || world < 1 || world > GROUP_MAX_RANKS || rank < 0 || rank >= world)
     return fail(PARALIA_ERR_INVALID_ARG, "bad group arguments (rank %d of %d)", rank, world);
-  Runtime& rt = Runtime::get();
-  PL_TRY(rt.init());
-  DeviceGuard guard;
-  PL_TRY(rt.ensure_device(dev));
   Group* g = new (std::nothrow) Group();
   if (!g) return fail(PARALIA_ERR_OUT_OF_MEMORY, "out of host memory");
   g->rank_ = rank;
   g->world_ = world;
-  g->dev_ = dev;
   device_grid(world, &g->d1_, &g->d2_);
   snprintf(g->shm_name_, sizeof(g->shm_name_), "/paralia_%s", name);
   g->shm_bytes_ = sizeof(Shm);
@@ -77,8 +80,9 @@ int Group::init(const char* name, int rank, int world, int dev) {
     fd = shm_open(g->shm_name_, O_CREAT | O_EXCL | O_RDWR, 0600);
     if (fd < 0 || ftruncate(fd, (off_t)g->shm_bytes_) != 0) {
       if (fd >= 0) close(fd);
+      const int rc = fail(PARALIA_ERR_CUDA, "cannot create the shared segment %s", g->shm_name_);
       delete g;
-      return fail(PARALIA_ERR_CUDA, "cannot create the shared segment %s", g->shm_name_);
+      return rc;
     }
   } else {
     while ((fd = shm_open(g->shm_name_, O_RDWR, 0600)) < 0) {
@@ -119,27 +123,79 @@ int Group::init(const char* name, int rank, int world, int dev) {
       usleep(200);
     }
   }
+  *out = g;
+  return PARALIA_OK;
+}
+
+void Group::detach(Group* g) {
+  if (g->shm_) munmap(g->shm_, g->shm_bytes_);
+  delete g;
+}
+
+int Group::init(const char* name, int rank, int world, int dev) {
+  if (g_group) return fail(PARALIA_ERR_INVALID_ARG, "a group is already initialised in this process");
+  if (!name || world < 1 || world > GROUP_MAX_RANKS || rank < 0 || rank >= world)
+    return fail(PARALIA_ERR_INVALID_ARG, "bad group arguments (rank %d of %d)", rank, world);
+  Runtime& rt = Runtime::get();
+  PL_TRY(rt.init());
+  DeviceGuard guard;
+  PL_TRY(rt.ensure_device(dev));
+  Group* g = nullptr;
+  PL_TRY(attach(name, rank, world, &g));
+  g->dev_ = dev;
   // Inter-process events, one per shareable tile slot, exported once.
-  PL_CUDA(cudaSetDevice(dev));
-  for (int i = 0; i < GROUP_MAX_EVENTS; ++i) {
-    PL_CUDA(cudaEventCreateWithFlags(&g->own_ev_[i], cudaEventDisableTiming | cudaEventInterprocess));
-    PL_CUDA(cudaIpcGetEventHandle(&g->shm_->ranks[rank].ev[i], g->own_ev_[i]));
+  cudaError_t ce = cudaSetDevice(dev);
+  for (int i = 0; i < GROUP_MAX_EVENTS && ce == cudaSuccess; ++i) {
+    ce = cudaEventCreateWithFlags(&g->own_ev_[i], cudaEventDisableTiming | cudaEventInterprocess);
+    if (ce == cudaSuccess) ce = cudaIpcGetEventHandle(&g->shm_->ranks[rank].ev[i], g->own_ev_[i]);
   }
+  if (ce != cudaSuccess) g->poison("a rank could not create its inter-process events");
   g->shm_->attached.fetch_add(1);
   g_group = g;
   int rc = g->barrier();
+  if (ce != cudaSuccess && rc == PARALIA_OK)
+    rc = fail(PARALIA_ERR_CUDA, "inter-process events: %s", cudaGetErrorString(ce));
   if (rank == 0) shm_unlink(g->shm_name_);  // every rank has it mapped (or never will)
   if (rc != PARALIA_OK) {
     // a rank never arrived: leave no half-built group behind
     for (int i = 0; i < GROUP_MAX_EVENTS; ++i)
       if (g->own_ev_[i]) cudaEventDestroy(g->own_ev_[i]);
-    munmap(g->shm_, g->shm_bytes_);
     cudaGetLastError();
-    delete g;
+    detach(g);
     g_group = nullptr;
     return rc;
   }
   return PARALIA_OK;
+}
+
+// The hand-shake layer alone, without CUDA: `rounds` barriers between `world` processes.
+// The rank named by fail_rank leaves at round fail_round: fail_mode 1 = it reports an error
+// of its own (as a collective call does when its arguments are bad), fail_mode 2 = it just
+// stops arriving. *waited_ms receives how long this rank spent in the barrier that failed.
+int Group::selftest_rendezvous(const char* name, int rank, int world, int rounds, int fail_rank,
+                               int fail_round, int fail_mode, double* waited_ms) {
+  Group* g = nullptr;
+  PL_TRY(attach(name, rank, world, &g));
+  int rc = PARALIA_OK;
+  if (waited_ms) *waited_ms = 0.0;
+  for (int r = 0; r < rounds && rc == PARALIA_OK; ++r) {
+    if (rank == fail_rank && r == fail_round) {
+      if (fail_mode == 1) {
+        rc = fail(PARALIA_ERR_INVALID_ARG, "injected failure of rank %d at round %d", rank, r);
+        g->poison(last_error_cstr());
+      } else {
+        rc = fail(PARALIA_ERR_UNSUPPORTED, "rank %d stops arriving at round %d", rank, r);
+      }
+      break;
+    }
+    const double t0 = wall_ms();
+    rc = g->barrier();
+    if (rc != PARALIA_OK && waited_ms) *waited_ms = wall_ms() - t0;
+  }
+  if (rank == 0) shm_unlink(g->shm_name_);
+  // a rank that leaves early keeps the segment mapped by its peers alive; nothing to wait for
+  detach(g);
+  return rc;
 }
 
 int Group::finalize() {
@@ -148,6 +204,9 @@ int Group::finalize() {
   DeviceGuard guard;
   cudaSetDevice(g->dev_);
   cudaDeviceSynchronize();
+  // In an abandoned group the two hand-shakes below fail at once; the peers have been told
+  // (every collective of theirs fails with the reason) and enqueue nothing that reads this
+  // rank's slab any more, and the slab itself stays allocated until PARALiA_dev_cache_free.
   g->barrier();   // nobody is still reading a peer's slab
   for (int p = 0; p < g->world_; ++p) {
     if (g->peer_slab_[p]) cudaIpcCloseMemHandle(g->peer_slab_[p]);
@@ -157,15 +216,39 @@ int Group::finalize() {
   g->barrier();   // every importer has closed its mappings before slabs may be freed
   for (int i = 0; i < GROUP_MAX_EVENTS; ++i)
     if (g->own_ev_[i]) cudaEventDestroy(g->own_ev_[i]);
-  munmap(g->shm_, g->shm_bytes_);
   cudaGetLastError();
-  delete g;
+  detach(g);
   g_group = nullptr;
   return PARALIA_OK;
 }
 
+void Group::poison(const char* why) {
+  if (!shm_) return;
+  uint32_t expected = 0;
+  if (shm_->poisoned.compare_exchange_strong(expected, 1u, std::memory_order_acq_rel)) {
+    shm_->poison_rank = rank_;
+    snprintf(shm_->poison_msg, sizeof(shm_->poison_msg), "%s", why ? why : "unspecified error");
+    shm_->poisoned.store(2u, std::memory_order_release);   // message complete
+  }
+}
+
+bool Group::poisoned() const {
+  return shm_ && shm_->poisoned.load(std::memory_order_acquire) != 0;
+}
+
+int Group::poisoned_error() const {
+  // give the poisoning rank a moment to finish writing its reason
+  for (int i = 0; i < 1000 && shm_->poisoned.load(std::memory_order_acquire) == 1u; ++i) usleep(10);
+  char msg[160];
+  snprintf(msg, sizeof(msg), "%s", shm_->poison_msg);
+  msg[sizeof(msg) - 1] = 0;
+  return fail(PARALIA_ERR_GROUP_FAILED, "rank %d: the process group was abandoned by rank %d (%s)",
+              rank_, (int)shm_->poison_rank, msg);
+}
+
 int Group::barrier() {
   if (world_ == 1) return PARALIA_OK;
+  if (poisoned()) return poisoned_error();
   const uint32_t gen = shm_->generation.load(std::memory_order_acquire);
   if (shm_->arrived.fetch_add(1, std::memory_order_acq_rel) + 1 == (uint32_t)world_) {
     shm_->arrived.store(0, std::memory_order_relaxed);
@@ -175,11 +258,25 @@ int Group::barrier() {
   const double t0 = wall_ms();
   uint32_t spins = 0;
   while (shm_->generation.load(std::memory_order_acquire) == gen) {
-    if ((++spins & 1023u) == 0) {
-      if (wall_ms() - t0 > BARRIER_TIMEOUT_MS)
-        return fail(PARALIA_ERR_TIMEOUT, "rank %d: a group barrier timed out (a rank is missing)",
-                    rank_);
-      usleep(20);
+    if ((++spins & 255u) == 0) {
+      if (poisoned()) {
+        shm_->arrived.fetch_sub(1, std::memory_order_acq_rel);
+        return poisoned_error();
+      }
+      if ((spins & 1023u) == 0) {
+        if (wall_ms() - t0 > BARRIER_TIMEOUT_MS) {
+          // take the arrival back and abandon the group: nobody may pass a later
+          // hand-shake on a counter that is one too high
+          char why[96];
+          snprintf(why, sizeof(why), "a hand-shake timed out after %.0f ms: a rank is missing",
+                   BARRIER_TIMEOUT_MS);
+          poison(why);
+          shm_->arrived.fetch_sub(1, std::memory_order_acq_rel);
+          return fail(PARALIA_ERR_TIMEOUT, "rank %d: a group barrier timed out (a rank is missing)",
+                      rank_);
+        }
+        usleep(20);
+      }
     }
   }
   return PARALIA_OK;

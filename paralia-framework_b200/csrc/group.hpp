@@ -34,14 +34,22 @@ class Group {
   static Group* current();   // null when no group is initialised
   static int init(const char* name, int rank, int world, int dev);
   static int finalize();
+  // The hand-shake layer alone (no CUDA): see group.cpp.
+  static int selftest_rendezvous(const char* name, int rank, int world, int rounds, int fail_rank,
+                                 int fail_round, int fail_mode, double* waited_ms);
 
   int rank() const { return rank_; }
   int world() const { return world_; }
   int dev() const { return dev_; }
   void grid(int* d1, int* d2) const { *d1 = d1_; *d2 = d2_; }
 
-  // Collective. Bounded wait: PARALIA_ERR_TIMEOUT when a rank does not arrive.
+  // Collective. Bounded wait: PARALIA_ERR_TIMEOUT when a rank does not arrive; the rank that
+  // times out abandons ("poisons") the group, after which every hand-shake of every rank
+  // fails at once with PARALIA_ERR_GROUP_FAILED and the reason.
   int barrier();
+  // Abandon the group because this rank failed where its peers expect it in a collective.
+  void poison(const char* why);
+  bool poisoned() const;
 
   // Collective start of a call: agree on sharing, (re)allocate the slab of `bytes` with
   // every importer's mapping closed first, exchange slab handles. On return *share_a /
@@ -58,7 +66,10 @@ class Group {
 
  private:
   Group() = default;
+  static int attach(const char* name, int rank, int world, Group** out);
+  static void detach(Group* g);
   int open_peer_slabs();
+  int poisoned_error() const;
   struct Shm;
   Shm* shm_ = nullptr;
   size_t shm_bytes_ = 0;

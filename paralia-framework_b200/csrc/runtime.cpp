@@ -2,6 +2,7 @@
 #include "runtime.hpp"
 
 #include <dlfcn.h>
+#include <unistd.h>
 
 #include <chrono>
 #include <cstdarg>
@@ -75,6 +76,29 @@ int Runtime::init() {
     }
   }
   return PARALIA_OK;
+}
+
+int wait_event_with_deadline(cudaEvent_t ev, double deadline_ms, int dev) {
+  const double t0 = wall_ms();
+  for (unsigned spins = 0;; ++spins) {
+    const cudaError_t e = cudaEventQuery(ev);
+    if (e == cudaSuccess) return PARALIA_OK;
+    if (e != cudaErrorNotReady)
+      return fail(PARALIA_ERR_CUDA, "GPU %d failed while running the plan: %s", dev, cudaGetErrorString(e));
+    if (wall_ms() - t0 > deadline_ms)
+      return fail(PARALIA_ERR_TIMEOUT, "GPU %d: the work of this call did not finish within its "
+                  "deadline of %.0f ms", dev, deadline_ms);
+    if (spins > 2000) usleep(50);   // the first milliseconds are polled without sleeping
+  }
+}
+
+double join_deadline_ms(double predicted_s) {
+  static const double forced = [] {
+    const char* e = getenv("PARALIA_JOIN_TIMEOUT_MS");
+    return e ? atof(e) : 0.0;
+  }();
+  if (forced > 0.0) return forced;
+  return std::max(120000.0, 50.0 * 1e3 * std::max(predicted_s, 0.0));
 }
 
 void HostPin::release() {

@@ -153,4 +153,11 @@ inline bool tma_addressable(const void* base, int64_t ld, int esz) {
 
 double wall_ms();
 
+// Wait on the host for `ev` (recorded on GPU `dev`) with a deadline: PARALIA_ERR_TIMEOUT when
+// it has not completed after deadline_ms, PARALIA_ERR_CUDA when the GPU reports an error.
+int wait_event_with_deadline(cudaEvent_t ev, double deadline_ms, int dev);
+// Deadline of a whole-problem call: PARALIA_JOIN_TIMEOUT_MS if set, else the larger of two
+// minutes and fifty times the predicted duration.
+double join_deadline_ms(double predicted_s);
+
 }  // namespace paralia

@@ -110,12 +110,16 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
 constexpr uint32_t SG_IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(SG_BN >> 3) << 17) |
                               ((uint32_t)(SG_BM >> 4) << 24);
 
+// The same with N = 128, for the half items.
+constexpr uint32_t SG_IDESC_HALF = (1u << 4) | (2u << 7) | (2u << 10) |
+                                   ((uint32_t)((SG_BN / 2) >> 3) << 17) | ((uint32_t)(SG_BM >> 4) << 24);
+
 __device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
-                                         uint32_t accumulate) {
+                                         uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(SG_IDESC), "r"(accumulate)
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 
@@ -147,6 +151,37 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// ------------------------------------------------------------------ work items
+// One work item of a persistent CTA: a 128 x 256 CTA tile, or one 128 x 128 half of it.
+struct SgItem {
+  int mt, nt;     // CTA tile coordinates (128-row strip, 256-column strip)
+  int half;       // -1: the whole tile; 0 / 1: its left / right 128 columns
+};
+
+// Items [0, whole) are whole CTA tiles, the rest are halves of the tiles that follow. CTA
+// tiles are numbered in panels of SG_PANEL column strips, inside a panel along the columns
+// first: the 148 CTAs of a round then share about 18 A strips and 8 B strips instead of all
+// A strips and 5 B strips, which cuts what a round pulls through L2.
+__device__ __forceinline__ SgItem sg_decode(const SgemmArgs& args, int item, int mtiles, int ntiles) {
+  SgItem w;
+  int tile;
+  if (item < args.whole_items) {
+    tile = item;
+    w.half = -1;
+  } else {
+    const int h = item - args.whole_items;
+    tile = args.whole_items + (h >> 1);
+    w.half = h & 1;
+  }
+  const int per_panel = mtiles * SG_PANEL;
+  const int panel = tile / per_panel;
+  const int width = min(SG_PANEL, ntiles - panel * SG_PANEL);
+  const int r = tile - panel * per_panel;
+  w.mt = r / width;
+  w.nt = panel * SG_PANEL + r % width;
+  return w;
+}
+
 // ------------------------------------------------------------------ GEMM kernel
 struct SgSmem {
   uint64_t full[SG_STAGES];
@@ -167,7 +202,7 @@ sgemm_tile_kernel(const __grid_constant__ SgemmArgs args) {
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int mtiles = (args.M + SG_BM - 1) / SG_BM, ntiles = (args.N + SG_BN - 1) / SG_BN;
-  const int tiles = mtiles * ntiles;
+  const int items = args.whole_items + args.half_items;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < SG_STAGES; ++s) {
@@ -204,8 +239,9 @@ sgemm_tile_kernel(const __grid_constant__ SgemmArgs args) {
     if (lane == 0) {
       int it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-        const int mt = tile % mtiles, nt = tile / mtiles;
+      for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
+        const SgItem w = sg_decode(args, item, mtiles, ntiles);
+        const int mt = w.mt, nt = w.nt;
         for (int p = 0; p < args.nparts && ok; ++p) {
           const SgemmKPart part = args.parts[p];
           const int kblocks = (part.klen + SG_BK - 1) / SG_BK;
@@ -223,9 +259,23 @@ sgemm_tile_kernel(const __grid_constant__ SgemmArgs args) {
               break;
             }
             unsigned char* st = smem + s * SG_STAGE_BYTES;
-            mbar_expect_tx(&ctl->full[s], SG_STAGE_BYTES);
-            bulk_load(st, a + (size_t)kb * SG_A_CHUNK, SG_A_CHUNK, &ctl->full[s]);
-            bulk_load(st + SG_A_CHUNK, b + (size_t)kb * SG_B_CHUNK, SG_B_CHUNK, &ctl->full[s]);
+            if (w.half < 0) {
+              mbar_expect_tx(&ctl->full[s], SG_STAGE_BYTES);
+              bulk_load(st, a + (size_t)kb * SG_A_CHUNK, SG_A_CHUNK, &ctl->full[s]);
+              bulk_load(st + SG_A_CHUNK, b + (size_t)kb * SG_B_CHUNK, SG_B_CHUNK, &ctl->full[s]);
+            } else {
+              // Half of the B strip: in each plane the 256 rows of one group of 4 k values
+              // are contiguous (4 KB), so the 128 rows of a half are eight 2 KB pieces (four
+              // k groups x hi / lo plane). They go to the places they have in a whole stage.
+              mbar_expect_tx(&ctl->full[s], SG_A_CHUNK + SG_B_CHUNK / 2);
+              bulk_load(st, a + (size_t)kb * SG_A_CHUNK, SG_A_CHUNK, &ctl->full[s]);
+              const unsigned char* bsrc = b + (size_t)kb * SG_B_CHUNK + (size_t)w.half * (SG_BN / 2) * 16;
+              unsigned char* bdst = st + SG_A_CHUNK + (size_t)w.half * (SG_BN / 2) * 16;
+#pragma unroll
+              for (int piece = 0; piece < 2 * (SG_BK / 4); ++piece)
+                bulk_load(bdst + piece * (SG_BN * 16), bsrc + piece * (SG_BN * 16), (SG_BN / 2) * 16,
+                          &ctl->full[s]);
+            }
           }
         }
       }
@@ -244,7 +294,10 @@ sgemm_tile_kernel(const __grid_constant__ SgemmArgs args) {
     if (lane == 0) {
       int it = 0, local_tile = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local_tile) {
+      for (int item = blockIdx.x; item < items && ok; item += gridDim.x, ++local_tile) {
+        const SgItem w = sg_decode(args, item, mtiles, ntiles);
+        const uint32_t idesc = w.half < 0 ? SG_IDESC : SG_IDESC_HALF;
+        const uint32_t b_half = w.half > 0 ? (uint32_t)((SG_BN / 2) * 16) : 0u;
         const int buf = local_tile & 1;
         if (local_tile >= 2 &&
             !mbar_wait_bounded(&ctl->acc_empty[buf], (uint32_t)(((local_tile >> 1) - 1) & 1),
@@ -265,7 +318,7 @@ sgemm_tile_kernel(const __grid_constant__ SgemmArgs args) {
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + s * SG_STAGE_BYTES);
           const uint32_t a_hi = sa, a_lo = sa + SG_A_CHUNK / 2;
-          const uint32_t b_hi = sa + SG_A_CHUNK, b_lo = b_hi + SG_B_CHUNK / 2;
+          const uint32_t b_hi = sa + SG_A_CHUNK + b_half, b_lo = b_hi + SG_B_CHUNK / 2;
           constexpr uint32_t LBO_A = SG_BM * 16, LBO_B = SG_BN * 16, SBO = 128;
 #pragma unroll
           for (int j = 0; j < SG_BK / 8; ++j) {
@@ -274,9 +327,9 @@ sgemm_tile_kernel(const __grid_constant__ SgemmArgs args) {
             const uint64_t dal = smem_desc(a_lo + j * 2 * LBO_A, LBO_A, SBO);
             const uint64_t dbh = smem_desc(b_hi + j * 2 * LBO_B, LBO_B, SBO);
             const uint64_t dbl = smem_desc(b_lo + j * 2 * LBO_B, LBO_B, SBO);
-            mma_tf32(d, dal, dbh, (ks > 0 || j > 0) ? 1u : 0u);   // small terms first
-            mma_tf32(d, dah, dbl, 1u);
-            mma_tf32(d, dah, dbh, 1u);
+            mma_tf32(d, dal, dbh, idesc, (ks > 0 || j > 0) ? 1u : 0u);   // small terms first
+            mma_tf32(d, dah, dbl, idesc, 1u);
+            mma_tf32(d, dah, dbh, idesc, 1u);
           }
           mma_commit(&ctl->empty[s]);   // the stage is free once these MMAs have read it
         }
@@ -292,9 +345,13 @@ sgemm_tile_kernel(const __grid_constant__ SgemmArgs args) {
     int local_tile = 0;
     bool ok = true;
     const bool zero_acc = stages_per_tile == 0;   // K == 0: the accumulator was never written
-    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local_tile) {
+    for (int item = blockIdx.x; item < items && ok; item += gridDim.x, ++local_tile) {
       const int buf = local_tile & 1;
-      const int mt = tile % mtiles, nt = tile / mtiles;
+      const SgItem w = sg_decode(args, item, mtiles, ntiles);
+      const int mt = w.mt, nt = w.nt;
+      // a half item's accumulator holds 128 columns, those of its half of the tile
+      const int n_base = nt * SG_BN + (w.half > 0 ? SG_BN / 2 : 0);
+      const int col_blocks = (w.half < 0 ? SG_BN : SG_BN / 2) / 32;
       if (!mbar_wait_bounded(&ctl->acc_full[buf], (uint32_t)((local_tile >> 1) & 1), abort_flag)) {
         if (!*abort_flag) { *abort_flag = 1; atomicExch(args.status, KERR_TMEM_WAIT_TIMEOUT); }
         ok = false;
@@ -303,7 +360,7 @@ sgemm_tile_kernel(const __grid_constant__ SgemmArgs args) {
       tc_fence_after();
       const int m = mt * SG_BM + quad * 32 + lane;
 #pragma unroll 1
-      for (int cb = 0; cb < SG_BN / 32; ++cb) {
+      for (int cb = 0; cb < col_blocks; ++cb) {
         uint32_t r[32];
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) +
                                (uint32_t)(buf * SG_BN + cb * 32);
@@ -311,7 +368,7 @@ sgemm_tile_kernel(const __grid_constant__ SgemmArgs args) {
         if (m < args.M) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            const int n = nt * SG_BN + cb * 32 + j;
+            const int n = n_base + cb * 32 + j;
             if (n < args.N) {
               float v = zero_acc ? 0.0f : alpha * __uint_as_float(r[j]);
               float* cp = args.C + m + (int64_t)n * args.ldc;
@@ -337,7 +394,102 @@ sgemm_tile_kernel(const __grid_constant__ SgemmArgs args) {
   }
 }
 
+// ------------------------------------------------------------------ TF32 peak loop
+// The MMA issue loop of the GEMM kernel without any global traffic: the operands of one
+// pipeline stage sit in shared memory for the whole run and `stages` times the six
+// tcgen05.mma of a stage (lo*hi, hi*lo, hi*hi for two K = 8 steps) are issued into the two
+// tensor-memory accumulators, committing to a ring of four barriers exactly like the GEMM
+// kernel does. What it measures is the rate the tensor pipe sustains for this instruction
+// shape (M = 128, N = 256, K = 8, operands read from shared memory through no-swizzle
+// K-major descriptors): the roofline of the 3xTF32 kernel is a third of it.
+__global__ void __launch_bounds__(64, 1) tf32_peak_kernel(int stages, int* status) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+  __shared__ uint64_t done[SG_STAGES];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < SG_STAGE_BYTES / 4; i += blockDim.x)
+    reinterpret_cast<float*>(smem)[i] = 1.0f;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < SG_STAGES; ++s) mbar_init(&done[s], 1);
+    abort_flag = 0;
+    tmem_slot = 0;
+    mbar_fence_init();
+  }
+  // the tensor core reads shared memory through the async proxy
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_slot)), "r"(512u)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  if (warp == 1 && lane == 0) {
+    const uint32_t sa = smem_u32(smem);
+    const uint32_t a_hi = sa, a_lo = sa + SG_A_CHUNK / 2;
+    const uint32_t b_hi = sa + SG_A_CHUNK, b_lo = b_hi + SG_B_CHUNK / 2;
+    constexpr uint32_t LBO_A = SG_BM * 16, LBO_B = SG_BN * 16, SBO = 128;
+    bool ok = true;
+    for (int it = 0; it < stages && ok; ++it) {
+      const int s = it % SG_STAGES;
+      if (it >= SG_STAGES &&
+          !mbar_wait_bounded(&done[s], (uint32_t)(((it / SG_STAGES) - 1) & 1), &abort_flag)) {
+        atomicExch(status, KERR_TMEM_WAIT_TIMEOUT);
+        ok = false;
+        break;
+      }
+      // a new accumulator every 256 stages, as a 4096-deep tile would
+      const uint32_t d = tmem_base + (uint32_t)(((it >> 8) & 1) * SG_BN);
+#pragma unroll
+      for (int j = 0; j < SG_BK / 8; ++j) {
+        const uint64_t dah = smem_desc(a_hi + j * 2 * LBO_A, LBO_A, SBO);
+        const uint64_t dal = smem_desc(a_lo + j * 2 * LBO_A, LBO_A, SBO);
+        const uint64_t dbh = smem_desc(b_hi + j * 2 * LBO_B, LBO_B, SBO);
+        const uint64_t dbl = smem_desc(b_lo + j * 2 * LBO_B, LBO_B, SBO);
+        mma_tf32(d, dal, dbh, SG_IDESC, ((it & 255) > 0 || j > 0) ? 1u : 0u);
+        mma_tf32(d, dah, dbl, SG_IDESC, 1u);
+        mma_tf32(d, dah, dbh, SG_IDESC, 1u);
+      }
+      mma_commit(&done[s]);
+    }
+    // everything issued has to finish before tensor memory is handed back
+    const int first = stages > SG_STAGES ? stages - SG_STAGES : 0;
+    for (int j = first; j < stages && ok; ++j) {
+      int zero = 0;
+      if (!mbar_wait_bounded(&done[j % SG_STAGES], (uint32_t)((j / SG_STAGES) & 1), &zero)) {
+        atomicExch(status, KERR_TMEM_WAIT_TIMEOUT);
+        ok = false;
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u)
+                 : "memory");
+  }
+}
+
 }  // namespace
+
+cudaError_t launch_tf32_peak(int stages, int blocks, int* status, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(tf32_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         SG_STAGE_BYTES + 256);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  tf32_peak_kernel<<<blocks, 64, SG_STAGE_BYTES + 256, stream>>>(stages, status);
+  return cudaGetLastError();
+}
 
 cudaError_t sgemm_tile_configure() {
   return cudaFuncSetAttribute(sgemm_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -357,10 +509,27 @@ cudaError_t launch_sgemm_pack(const float* src, int64_t ld, bool k_contig, int r
   return cudaGetLastError();
 }
 
-cudaError_t launch_sgemm_tile(const SgemmArgs& args, int sm_count, cudaStream_t stream) {
-  const int tiles = ((args.M + SG_BM - 1) / SG_BM) * ((args.N + SG_BN - 1) / SG_BN);
-  if (tiles == 0) return cudaSuccess;
-  const int grid = tiles < sm_count ? tiles : sm_count;
+void sgemm_tile_schedule(int M, int N, int sms, int* whole_items, int* half_items, int* grid) {
+  const int tiles = ((M + SG_BM - 1) / SG_BM) * ((N + SG_BN - 1) / SG_BN);
+  const int G = sms > 0 ? sms : 1;
+  int whole = (tiles / G) * G;
+  const int rest = tiles - whole;
+  int halves = 0;
+  // What is left after the last whole round of the grid is cut into halves when those fit
+  // into one more round: that round then takes half the time of a whole-tile round.
+  if (rest > 0 && 2 * rest <= G) halves = 2 * rest;
+  else whole += rest;
+  *whole_items = whole;
+  *half_items = halves;
+  const int items = whole + halves;
+  *grid = items < G ? items : G;
+}
+
+cudaError_t launch_sgemm_tile(const SgemmArgs& args_in, int sm_count, cudaStream_t stream) {
+  SgemmArgs args = args_in;
+  int grid = 0;
+  sgemm_tile_schedule(args.M, args.N, sm_count, &args.whole_items, &args.half_items, &grid);
+  if (grid == 0) return cudaSuccess;
   sgemm_tile_kernel<<<grid, SG_THREADS, SG_SMEM_BYTES, stream>>>(args);
   return cudaGetLastError();
 }

@@ -21,6 +21,7 @@ constexpr int SG_B_CHUNK = SG_BN * SG_BK * 4 * 2;   // hi + lo plane of a B stag
 constexpr int SG_STAGE_BYTES = SG_A_CHUNK + SG_B_CHUNK;
 constexpr int SG_SMEM_BYTES = SG_STAGES * SG_STAGE_BYTES + 1024;
 constexpr int SG_MAX_PARTS = 64;
+constexpr int SG_PANEL = 8;      // column strips per panel of the CTA tile numbering
 
 // Bytes of the packed form of a tile with `rows` rows and `klen` k values, for an operand
 // packed in blocks of `rb` rows (SG_BM for A, SG_BN for B).
@@ -50,10 +51,22 @@ struct SgemmArgs {
   int32_t M, N;
   int32_t nparts;
   int* status;
+  // Work items, filled in by launch_sgemm_tile (sgemm_tile_schedule): whole CTA tiles, then
+  // halves of the CTA tiles that follow.
+  int32_t whole_items, half_items;
   SgemmKPart parts[SG_MAX_PARTS];
 };
 
+// The static work list of a launch over an M x N C tile on a GPU with `sms` SMs.
+void sgemm_tile_schedule(int M, int N, int sms, int* whole_items, int* half_items, int* grid);
+
 cudaError_t launch_sgemm_tile(const SgemmArgs& args, int sm_count, cudaStream_t stream);
+
+// Tensor-pipe throughput loop of the GEMM kernel's MMA shape on shared-memory-resident
+// operands: every block issues `stages` x 6 tcgen05.mma.kind::tf32 of 128 x 256 x 8
+// (2 * 128 * 256 * 8 flop each). `status` receives a KERR_* code if a wait gives up.
+cudaError_t launch_tf32_peak(int stages, int blocks, int* status, cudaStream_t stream);
+constexpr double SG_PEAK_FLOP_PER_STAGE = 6.0 * 2.0 * SG_BM * SG_BN * 8;
 
 // Opt the kernels into their dynamic shared memory size; once per device.
 cudaError_t sgemm_tile_configure();

@@ -62,3 +62,22 @@ def test_missing_rank_is_reported_by_a_bounded_barrier(pl, tmp_path):
     assert int(code) == pl.ERR_TIMEOUT
     assert 1.0 < float(secs) < 30.0
     assert float(dot) == 1024.0
+
+
+def test_host_join_has_a_deadline(pl):
+    """The whole-problem routines join their GPUs by waiting for an end event with a deadline.
+    A kernel that ends by itself after 300 ms is queued; a join with a 50 ms deadline must come
+    back with a time-out (instead of blocking) and the context must stay usable."""
+    import time
+    pl.init()
+    t0 = time.perf_counter()
+    with pytest.raises(pl.ParaliaError) as e:
+        pl.selftest_join_deadline(0, 300.0, 50.0)
+    dt = time.perf_counter() - t0
+    assert e.value.code == pl.ERR_TIMEOUT and "deadline" in str(e.value)
+    assert dt < 5.0
+    # a deadline longer than the kernel: the join succeeds
+    pl.selftest_join_deadline(0, 20.0, 5000.0)
+    x = np.ones(4096)
+    d, _ = pl.ddot(4096, x, 1, x, 1, 0.0, ctl=pl.make_ctl(units=[0]))
+    assert d == 4096.0
