@@ -180,6 +180,17 @@ int PARALiA_ddot(int64_t N, const double* x, int64_t incx, int locx,
                  const double* y, int64_t incy, int locy, double* result,
                  const paralia_ctl* ctl, paralia_report* out);
 
+/* The same dot product, but the per-tile sums are returned in tile order instead of being
+ * added up: tile_sums[i] = sum over tile i (tile length = out->T, ctl->T if given), *count =
+ * number of tiles (at most `capacity` are written; pass capacity 0 to ask for the count).
+ * Adding them in order to a start value gives PARALiA_ddot's result bit for bit. This is
+ * what lets several processes, each holding a run of whole tiles of the vectors, combine
+ * their parts in the one global tile order (reference: the host-side sum, ddot.cpp:431). */
+int PARALiA_ddot_tiles(int64_t N, const double* x, int64_t incx, int locx,
+                       const double* y, int64_t incy, int locy,
+                       double* tile_sums, int64_t capacity, int64_t* count,
+                       const paralia_ctl* ctl, paralia_report* out);
+
 /* ---- one process per GPU ------------------------------------------------------------
  * The reference drives all GPUs from one process. Under a launcher that starts one
  * process per GPU, the processes form a group: rank = r*D2 + c of the D1 x D2 device grid

@@ -130,6 +130,8 @@ SIGNATURES = {
     "PARALiA_daxpy": (C.c_int, [_i64, _dbl, _vp, _i64, C.c_int, _vp, _i64, C.c_int, _ctl_p, _rep_p]),
     "PARALiA_ddot": (C.c_int, [_i64, _vp, _i64, C.c_int, _vp, _i64, C.c_int, C.POINTER(_dbl),
                                _ctl_p, _rep_p]),
+    "PARALiA_ddot_tiles": (C.c_int, [_i64, _vp, _i64, C.c_int, _vp, _i64, C.c_int, C.POINTER(_dbl), _i64,
+                                     C.POINTER(_i64), _ctl_p, _rep_p]),
     "PARALiA_group_init": (C.c_int, [C.c_char_p, C.c_int, C.c_int, C.c_int]),
     "PARALiA_group_finalize": (C.c_int, []),
     "PARALiA_group_dgemm": (C.c_int, [_chr, _chr, _i64, _i64, _i64, _dbl, _vp, _i64, C.c_int, _vp,
@@ -343,6 +345,19 @@ def ddot(N, x, incx, y, incy, result: float = 0.0, locx=LOC_AUTO, locy=LOC_AUTO,
     _check(lib().PARALiA_ddot(N, _ptr(x), incx, locx, _ptr(y), incy, locy, C.byref(res),
                               C.byref(ctl) if ctl is not None else None, C.byref(rep)))
     return res.value, rep
+
+
+def ddot_tiles(N, x, incx, y, incy, locx=LOC_AUTO, locy=LOC_AUTO, ctl: Ctl | None = None):
+    """Per-tile sums of a DDOT in tile order (``PARALiA_ddot_tiles``). Returns (list, report)."""
+    rep = Report()
+    cap = max(1, -(-N // (ctl.T if ctl is not None and ctl.T > 0 else 1 << 16)))
+    buf = (C.c_double * cap)()
+    cnt = _i64()
+    _check(lib().PARALiA_ddot_tiles(N, _ptr(x), incx, locx, _ptr(y), incy, locy, buf, cap, C.byref(cnt),
+                                    C.byref(ctl) if ctl is not None else None, C.byref(rep)))
+    if cnt.value > cap:
+        raise ParaliaError(ERR_INVALID_ARG, f"{cnt.value} tiles do not fit the buffer of {cap}")
+    return list(buf[:cnt.value]), rep
 
 
 def tile_dgemm(dev, TransA, TransB, M, N, K, alpha, A, ldA, B, ldB, beta, Cm, ldC,

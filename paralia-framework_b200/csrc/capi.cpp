@@ -104,6 +104,12 @@ int PARALiA_ddot(int64_t N, const double* x, int64_t incx, int locx, const doubl
   return exec_ddot(N, x, incx, locx, y, incy, locy, result, ctl, out);
 }
 
+int PARALiA_ddot_tiles(int64_t N, const double* x, int64_t incx, int locx, const double* y,
+                       int64_t incy, int locy, double* tile_sums, int64_t capacity, int64_t* count,
+                       const paralia_ctl* ctl, paralia_report* out) {
+  return exec_ddot_tiles(N, x, incx, locx, y, incy, locy, tile_sums, capacity, count, ctl, out);
+}
+
 int PARALiA_group_init(const char* name, int rank, int world, int dev) {
   return Group::init(name, rank, world, dev);
 }

@@ -39,4 +39,10 @@ int exec_daxpy(int64_t N, double alpha, const double* x, int64_t incx, int locx,
 int exec_ddot(int64_t N, const double* x, int64_t incx, int locx, const double* y, int64_t incy,
               int locy, double* result, const paralia_ctl* ctl, paralia_report* out);
 
+// The per-tile sums of a DDOT in tile order instead of their total (for callers that combine
+// tiles computed by several processes in one global order).
+int exec_ddot_tiles(int64_t N, const double* x, int64_t incx, int locx, const double* y,
+                    int64_t incy, int locy, double* tile_sums, int64_t capacity, int64_t* count,
+                    const paralia_ctl* ctl, paralia_report* out);
+
 }  // namespace paralia

@@ -61,13 +61,15 @@ int fetch_vec(double* dst, const VecDesc& v, int64_t start, int64_t len, cudaStr
 // is_dot == false: y <- alpha*x + y;  is_dot == true: *result += x . y
 int run_level1(bool is_dot, int64_t N, double alpha, const double* x, int64_t incx, int locx,
                double* y, int64_t incy, int locy, double* result, const paralia_ctl* ctl,
-               paralia_report* out) {
+               paralia_report* out, double* tile_sums = nullptr, int64_t tile_capacity = 0,
+               int64_t* tile_count = nullptr) {
   const double t_call0 = wall_ms();
   paralia_report local_rep;
   paralia_report* rep = out ? out : &local_rep;
   memset(rep, 0, sizeof(*rep));
   if (N < 0) return fail(PARALIA_ERR_INVALID_ARG, "negative vector length");
-  if (is_dot && !result) return fail(PARALIA_ERR_INVALID_ARG, "NULL result pointer");
+  if (is_dot && !result && !tile_count) return fail(PARALIA_ERR_INVALID_ARG, "NULL result pointer");
+  if (tile_count) *tile_count = 0;
   if (N == 0) return PARALIA_OK;
   if (!x || !y) return fail(PARALIA_ERR_INVALID_ARG, "NULL vector");
   if (incx <= 0 || incy <= 0)
@@ -268,13 +270,18 @@ int run_level1(bool is_dot, int64_t N, double alpha, const double* x, int64_t in
   if (rc == PARALIA_OK && is_dot) {
     // Partials are added into *result in tile order; *result is not zeroed first
     // (ddot.cpp:431).
-    double acc = *result;
+    double acc = result ? *result : 0.0;
+    int64_t t = 0;
     for (int ui = 0; ui < U; ++ui) {
       const DeviceCtx& dc = rt.dev(units[ui].dev);
       const int64_t n = units[ui].tile_hi - units[ui].tile_lo;
-      for (int64_t j = 0; j < n; ++j) acc += dc.dot_results_host[j];
+      for (int64_t j = 0; j < n; ++j, ++t) {
+        acc += dc.dot_results_host[j];
+        if (tile_sums && t < tile_capacity) tile_sums[t] = dc.dot_results_host[j];
+      }
     }
-    *result = acc;
+    if (result) *result = acc;
+    if (tile_count) *tile_count = t;
   }
   cleanup();
   rep->device_ms = dev_ms;
@@ -293,6 +300,15 @@ int exec_ddot(int64_t N, const double* x, int64_t incx, int locx, const double* 
               int locy, double* result, const paralia_ctl* ctl, paralia_report* out) {
   return run_level1(true, N, 0.0, x, incx, locx, const_cast<double*>(y), incy, locy, result, ctl,
                     out);
+}
+
+int exec_ddot_tiles(int64_t N, const double* x, int64_t incx, int locx, const double* y,
+                    int64_t incy, int locy, double* tile_sums, int64_t capacity, int64_t* count,
+                    const paralia_ctl* ctl, paralia_report* out) {
+  if (!count || capacity < 0 || (capacity > 0 && !tile_sums))
+    return fail(PARALIA_ERR_INVALID_ARG, "bad tile-sum buffer");
+  return run_level1(true, N, 0.0, x, incx, locx, const_cast<double*>(y), incy, locy, nullptr, ctl,
+                    out, tile_sums, capacity, count);
 }
 
 }  // namespace paralia

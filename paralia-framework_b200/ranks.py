@@ -71,3 +71,35 @@ def allreduce_sum(value: float, device=None) -> float:
     for p in parts:            # rank order
         total += float(p.item())
     return total
+
+
+def ddot_tiles_in_order(tile_sums, start: float = 0.0, device=None) -> float:
+    """DDOT across ranks, bit-equal to the single-process result. Every rank holds a contiguous
+    run of WHOLE tiles of the vectors (``vector_chunk`` with quantum = the tile length) and
+    passes the per-tile sums of its run (``ddot_tiles``). The runs are gathered in rank order,
+    which is the global tile order, and added one tile after the other to ``start`` on every
+    rank -- exactly the sequence of additions the library performs when one process owns the
+    whole vector (reference: the host-side sum in tile order, ddot.cpp:431)."""
+    import torch
+    import torch.distributed as dist
+
+    mine = [float(v) for v in tile_sums]
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        runs = [mine]
+    else:
+        world = dist.get_world_size()
+        n = torch.tensor([len(mine)], dtype=torch.int64, device=device)
+        counts = [torch.empty_like(n) for _ in range(world)]
+        dist.all_gather(counts, n)
+        longest = max(int(c.item()) for c in counts)
+        pad = torch.zeros(max(longest, 1), dtype=torch.float64, device=device)
+        if mine:
+            pad[:len(mine)] = torch.tensor(mine, dtype=torch.float64, device=device)
+        parts = [torch.empty_like(pad) for _ in range(world)]
+        dist.all_gather(parts, pad)
+        runs = [p[:int(c.item())].tolist() for p, c in zip(parts, counts)]
+    acc = float(start)
+    for run in runs:              # rank order = global tile order
+        for v in run:
+            acc += v
+    return acc

@@ -1,11 +1,16 @@
 """In-process multi-GPU path (the library drives several GPUs from one process, like
 the reference): 2D block ownership of C, home-GPU host fetch plus NVLink forwarding,
 operands spread over different GPUs. Needs at least two GPUs."""
+import os
+import sys
+from pathlib import Path
+
 import numpy as np
 import pytest
 
 pytestmark = pytest.mark.gpu
 EPS64 = 2.0 ** -52
+ROOT = Path(__file__).resolve().parent.parent
 
 
 def _ngpu():
@@ -164,3 +169,60 @@ def test_dgemm_four_gpus_grid(pl, orc):
     szA, szB, szC = M * K * 8, K * N * 8, M * N * 8
     assert rep.h2d_bytes == szA + szB + szC      # every host tile crosses a host link once
     assert rep.p2p_bytes == szA + szB            # and is forwarded to one grid neighbour
+
+
+def _l1_rank(rank, world, port, n, T, out_dir):
+    """One process per GPU over NCCL: vectors pre-split across the GPUs (BASELINE configs[4])."""
+    sys.path.insert(0, str(ROOT))
+    import importlib
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as entry
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(f"cuda:{rank}"))
+    pl = entry.load_package()
+    ranks = importlib.import_module("paralia_framework_b200.ranks")
+    lo, hi = ranks.vector_chunk(rank, world, n, quantum=T)
+    m = hi - lo
+    # the rank's chunk of the seeded global vectors, resident on its own GPU
+    x = torch.empty(n, dtype=torch.float64, device=f"cuda:{rank}")
+    y = torch.empty(n, dtype=torch.float64, device=f"cuda:{rank}")
+    pl.fill_f64(x, n, 42, 0, rank)
+    pl.fill_f64(y, n, 43, 0, rank)
+    xc, yc = x[lo:hi].clone(), y[lo:hi].clone()
+    ctl = pl.make_ctl(T=T, units=[rank])
+    sums, _ = pl.ddot_tiles(m, xc, 1, yc, 1, locx=rank, locy=rank, ctl=ctl)
+    dot = ranks.ddot_tiles_in_order(sums, start=0.0, device=f"cuda:{rank}")
+    pl.daxpy(m, -0.5, xc, 1, yc, 1, locx=rank, locy=rank, ctl=ctl)
+    torch.cuda.synchronize()
+    np.save(os.path.join(out_dir, f"l1_{rank}.npy"), np.array([dot, lo, hi]))
+    np.save(os.path.join(out_dir, f"y_{rank}.npy"), yc.cpu().numpy())
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_level1_presplit_ranks_bit_equal_to_one_gpu(pl, tmp_path):
+    """DAXPY and DDOT with the vectors pre-split over one process per GPU: the chunk results
+    and the dot product, combined in global tile order, equal the one-GPU call bit for bit."""
+    import torch
+    import torch.multiprocessing as mp
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs two GPUs")
+    n, T = (1 << 24) + 12345, 1 << 20
+    port = 29700 + os.getpid() % 2000
+    mp.spawn(_l1_rank, args=(world, port, n, T, str(tmp_path)), nprocs=world, join=True)
+    x = torch.empty(n, dtype=torch.float64, device="cuda:0")
+    y = torch.empty(n, dtype=torch.float64, device="cuda:0")
+    pl.fill_f64(x, n, 42, 0, 0)
+    pl.fill_f64(y, n, 43, 0, 0)
+    ctl = pl.make_ctl(T=T, units=[0])
+    want_dot, _ = pl.ddot(n, x, 1, y, 1, 0.0, locx=0, locy=0, ctl=ctl)
+    pl.daxpy(n, -0.5, x, 1, y, 1, locx=0, locy=0, ctl=ctl)
+    want_y = y.cpu().numpy()
+    for r in range(world):
+        dot, lo, hi = np.load(tmp_path / f"l1_{r}.npy")
+        assert float(dot) == want_dot                      # every rank holds the same, exact bits
+        assert np.array_equal(np.load(tmp_path / f"y_{r}.npy"), want_y[int(lo):int(hi)])

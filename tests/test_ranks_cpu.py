@@ -44,6 +44,16 @@ def _worker(rank, world, port, M, N, K, nvec, out_dir):
     part, _ = orc.ddot_tiled(hi - lo, x[lo:], 1, y[lo:], 1, 128, 0.0)
     total = ranks.allreduce_sum(part)
     np.save(os.path.join(out_dir, f"dot_rank{rank}.npy"), np.array([part, total]))
+    # the bit-exact form: runs of whole tiles per rank, per-tile sums combined in tile order
+    T = 128
+    tlo, thi = ranks.vector_chunk(rank, world, nvec, quantum=T)
+    sums = []
+    for s0 in range(tlo, thi, T):
+        n_t = min(T, thi - s0)
+        v, _ = orc.ddot_tiled(n_t, x[s0:], 1, y[s0:], 1, T, 0.0)
+        sums.append(v)
+    exact = ranks.ddot_tiles_in_order(sums, start=0.25)
+    np.save(os.path.join(out_dir, f"dot_exact_rank{rank}.npy"), np.array([exact]))
     cover = torch.zeros(nvec, dtype=torch.int32)
     cover[lo:hi] += 1
     dist.all_reduce(cover)
@@ -78,6 +88,10 @@ def test_rank_partition_reassembles_whole_problem(orc, tmp_path, world):
     for part, _ in per_rank:
         ordered += float(part)
     assert all(float(total) == ordered for _, total in per_rank)
+    # per-tile sums combined in the global tile order: the single-process bits, on every rank
+    whole, _ = orc.ddot_tiled(nvec, x, 1, y, 1, 128, 0.25)
+    for r in range(world):
+        assert float(np.load(tmp_path / f"dot_exact_rank{r}.npy")[0]) == whole
 
 
 def test_gemm_block_grid_matches_library(pl):
