@@ -248,6 +248,12 @@ int PARALiA_selftest_group_rendezvous(const char* name, int rank, int world, int
  * (Database_builder/CuCuBLAS/src/dgemm_microbench.cu:141-142). All pointers are device
  * pointers on GPU `dev`; `stream` is a cudaStream_t (NULL = the legacy default stream).
  * Asynchronous: the caller synchronises the stream. */
+/* The tile kernels bound every wait inside them; a wait that runs out makes the kernel stop
+ * and leave a code in a per-GPU status word. The asynchronous tile entry points cannot
+ * report that themselves: after synchronising the stream, PARALiA_tile_status(dev) reads and
+ * clears the word (it synchronises the GPU) and returns PARALIA_ERR_TIMEOUT if a tile kernel
+ * gave up since the last check. The whole-problem routines do this check on their own. */
+int PARALiA_tile_status(int dev);
 int PARALiA_tile_dgemm(int dev, void* stream, char TransA, char TransB,
                        int64_t M, int64_t N, int64_t K, double alpha,
                        const double* A, int64_t ldA, const double* B, int64_t ldB,

@@ -139,6 +139,7 @@ SIGNATURES = {
     "PARALiA_group_sgemm": (C.c_int, [_chr, _chr, _i64, _i64, _i64, _flt, _vp, _i64, C.c_int, _vp,
                                       _i64, C.c_int, _flt, _vp, _i64, C.c_int, _ctl_p, _rep_p]),
     "PARALiA_selftest_bounded_wait": (C.c_int, [C.c_int, _dbl]),
+    "PARALiA_tile_status": (C.c_int, [C.c_int]),
     "PARALiA_tile_dgemm": (C.c_int, [C.c_int, _vp, _chr, _chr, _i64, _i64, _i64, _dbl, _vp, _i64,
                                      _vp, _i64, _dbl, _vp, _i64]),
     "PARALiA_tile_sgemm": (C.c_int, [C.c_int, _vp, _chr, _chr, _i64, _i64, _i64, _flt, _vp, _i64,
@@ -365,6 +366,11 @@ def tile_dgemm(dev, TransA, TransB, M, N, K, alpha, A, ldA, B, ldB, beta, Cm, ld
     """Reference: backend_run_operation(params, "Dgemm", queue) (Subkernel.cpp:168,228)."""
     _check(lib().PARALiA_tile_dgemm(dev, stream, _c(TransA), _c(TransB), M, N, K, alpha, _ptr(A),
                                     ldA, _ptr(B), ldB, beta, _ptr(Cm), ldC))
+
+
+def tile_status(dev) -> None:
+    """Raises ParaliaError(ERR_TIMEOUT) if a tile kernel on `dev` gave up on a wait."""
+    _check(lib().PARALiA_tile_status(dev))
 
 
 def tile_sgemm(dev, TransA, TransB, M, N, K, alpha, A, ldA, B, ldB, beta, Cm, ldC,

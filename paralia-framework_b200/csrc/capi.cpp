@@ -168,6 +168,14 @@ int PARALiA_tile_dgemm(int dev, void* stream, char TransA, char TransB, int64_t 
   return PARALIA_OK;
 }
 
+int PARALiA_tile_status(int dev) {
+  Runtime& rt = Runtime::get();
+  PL_TRY(rt.init());
+  if (dev < 0 || dev >= rt.device_count()) return fail(PARALIA_ERR_INVALID_ARG, "GPU id %d out of range", dev);
+  DeviceGuard guard;
+  return rt.check_status(dev);
+}
+
 int PARALiA_tile_sgemm(int dev, void* stream, char TransA, char TransB, int64_t M, int64_t N,
                        int64_t K, float alpha, const float* A, int64_t ldA, const float* B,
                        int64_t ldB, float beta, float* C, int64_t ldC) {

@@ -38,6 +38,9 @@ int sm_count_of(int dev);   // sgemm_exec.cpp
 namespace {
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+inline size_t matrix_span_bytes(int64_t ld, int64_t rows, int64_t cols, int esz) {
+  return (rows <= 0 || cols <= 0) ? 0 : (size_t)(ld * (cols - 1) + rows) * esz;
+}
 inline int64_t round_up(int64_t a, int64_t b) { return ceil_div(a, b) * b; }
 
 // Which unit pulls a host-resident A tile (mi, ki) or B tile (ki, ni) over its host link
@@ -759,13 +762,14 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
   double pin_ms = 0.0;
   int rc = PARALIA_OK;
   if (K > 0) {
-    rc = resolve_operand(&g.A, locA, (size_t)g.A.ld * g.A.cols * g.esz, ngpu, &pin_ms);
+    // a column-major matrix spans ld*(cols-1) + rows elements, not ld*cols
+    rc = resolve_operand(&g.A, locA, matrix_span_bytes(g.A.ld, g.A.rows, g.A.cols, g.esz), ngpu, &pin_ms);
     if (rc == PARALIA_OK)
-      rc = resolve_operand(&g.B, locB, (size_t)g.B.ld * g.B.cols * g.esz, ngpu, &pin_ms);
+      rc = resolve_operand(&g.B, locB, matrix_span_bytes(g.B.ld, g.B.rows, g.B.cols, g.esz), ngpu, &pin_ms);
   } else {
     g.A.loc = g.B.loc = -1;
   }
-  if (rc == PARALIA_OK) rc = resolve_operand(&g.C, locC, (size_t)g.C.ld * N * g.esz, ngpu, &pin_ms);
+  if (rc == PARALIA_OK) rc = resolve_operand(&g.C, locC, matrix_span_bytes(g.C.ld, M, N, g.esz), ngpu, &pin_ms);
   const bool keep_pinned = ctl && (ctl->flags & PARALIA_FLAG_KEEP_PINNED);
   auto cleanup_pins = [&]() {
     if (!keep_pinned) { unpin(&g.A); unpin(&g.B); unpin(&g.C); }

@@ -126,7 +126,8 @@ int gemv_n_slices(int rows, int cols) {
 cudaError_t launch_dgemv_tile(bool trans, int rows, int cols, double alpha, const double* A,
                               int64_t lda, const double* x, int64_t incx, double beta, double* y,
                               int64_t incy, double* partial, cudaStream_t stream, int* launches) {
-  if (rows <= 0 || cols <= 0) return cudaSuccess;
+  // a transposed tile without rows still scales y by beta (every dot product is empty)
+  if (cols <= 0 || rows < 0 || (rows == 0 && !trans)) return cudaSuccess;
   const bool a_ok = (reinterpret_cast<uintptr_t>(A) & 15) == 0 && (lda & 1) == 0;
   if (!trans) {
     const int slices = gemv_n_slices(rows, cols);

@@ -55,8 +55,13 @@ int exec_dgemv(char TransA, int64_t M, int64_t N, double alpha, const double* A,
   const int64_t out_len = trans ? N : M, in_len = trans ? M : N;
   if (out_len == 0) return PARALIA_OK;
   if (!y || (in_len > 0 && (!A || !x))) return fail(PARALIA_ERR_INVALID_ARG, "NULL operand");
-  if (in_len == 0)   // y <- beta*y, written as y <- (beta-1)*y + y
-    return exec_daxpy(out_len, beta - 1.0, y, incy, locy, y, incy, locy, ctl, out);
+  if (in_len == 0 && !(trans && M == 0)) {
+    // Nothing to multiply: y <- beta*y (y <- 0 for beta == 0, without reading y, as BLAS
+    // defines it). Run as the transposed product of a matrix with no rows: every column's
+    // dot product is empty and the kernel's epilogue applies beta in one rounding. A and x
+    // are never read; y's own pointer stands in for them. (That call falls through here.)
+    return exec_dgemv('T', 0, out_len, alpha, y, 1, locy, y, 1, locy, beta, y, incy, locy, ctl, out);
+  }
 
   Runtime& rt = Runtime::get();
   PL_TRY(rt.init());
@@ -67,7 +72,7 @@ int exec_dgemv(char TransA, int64_t M, int64_t N, double alpha, const double* A,
   HostPin pins[3];
   double pin_ms = 0.0;
   int lA = -1, lx = -1, ly = -1;
-  int rc = resolve_operand_location(A, locA, (size_t)ldA * N * 8, ngpu, &lA, &pins[0], &pin_ms);
+  int rc = resolve_operand_location(A, locA, (M > 0 && N > 0) ? (size_t)(ldA * (N - 1) + M) * 8 : 0, ngpu, &lA, &pins[0], &pin_ms);
   if (rc == PARALIA_OK) rc = resolve_operand_location(x, locx, (size_t)(1 + (in_len - 1) * incx) * 8, ngpu, &lx, &pins[1], &pin_ms);
   if (rc == PARALIA_OK) rc = resolve_operand_location(y, locy, (size_t)(1 + (out_len - 1) * incy) * 8, ngpu, &ly, &pins[2], &pin_ms);
   const bool keep_pinned = ctl && (ctl->flags & PARALIA_FLAG_KEEP_PINNED);
@@ -182,7 +187,7 @@ int exec_dgemv(char TransA, int64_t M, int64_t N, double alpha, const double* A,
       else if (loc == u.dev) rep->d2d_bytes += bytes;
       else rep->p2p_bytes += bytes;
     };
-    if (!x_here) {
+    if (!x_here && in_len > 0) {
       cudaStream_t cs = lx == -1 ? dc.h2d : dc.p2p;
       if (incx == 1) PL_CUDA(cudaMemcpyAsync(u.x_dev, x, in_len * 8, cudaMemcpyDefault, cs));
       else PL_CUDA(cudaMemcpy2DAsync(u.x_dev, 8, x, incx * 8, 8, in_len, cudaMemcpyDefault, cs));
@@ -208,7 +213,7 @@ int exec_dgemv(char TransA, int64_t M, int64_t N, double alpha, const double* A,
       const double* a_src = trans ? A + (u.o_lo + c0) * ldA : A + u.o_lo + c0 * ldA;
       const double* a_tile = a_src;
       int64_t lda_tile = ldA;
-      if (!a_here) {
+      if (!a_here && rows > 0) {
         const int slot = (int)(j & 1);
         cudaStream_t cs = lA == -1 ? dc.h2d : dc.p2p;
         if (u.slot_free[slot]) PL_CUDA(cudaStreamWaitEvent(cs, u.slot_free[slot], 0));

@@ -120,17 +120,30 @@ int resolve_operand_location(const void* ptr, int loc_in, size_t bytes, int ngpu
     return fail(PARALIA_ERR_INVALID_ARG, "operand declared on the host but the pointer is on GPU %d",
                 actual);
   *loc_out = loc;
-  if (loc == -1 && !pinned && bytes > 0) {
-    const double t0 = wall_ms();
-    cudaError_t e = cudaHostRegister(const_cast<void*>(ptr), bytes, cudaHostRegisterPortable);
-    if (e != cudaSuccess) {
-      cudaGetLastError();
-      return fail(PARALIA_ERR_CUDA, "cannot page-lock a host operand of %zu bytes: %s", bytes,
-                  cudaGetErrorString(e));
+  if (loc == -1 && bytes > 0) {
+    // Page-locked only if both ends are: an operand that is a sub-view of a larger matrix can
+    // start inside a range someone registered and run past its end.
+    bool tail_pinned = pinned;
+    if (pinned && bytes > 1)
+      pointer_location(static_cast<const char*>(ptr) + bytes - 1, &tail_pinned);
+    if (!(pinned && tail_pinned)) {
+      const double t0 = wall_ms();
+      cudaError_t e = pinned ? cudaErrorHostMemoryAlreadyRegistered
+                             : cudaHostRegister(const_cast<void*>(ptr), bytes, cudaHostRegisterPortable);
+      if (e == cudaErrorHostMemoryAlreadyRegistered) {
+        // Overlaps a range that is registered already (interleaved views of one parent): the
+        // operand is used as pageable memory, which is correct, only slower.
+        cudaGetLastError();
+      } else if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(PARALIA_ERR_CUDA, "cannot page-lock a host operand of %zu bytes: %s", bytes,
+                    cudaGetErrorString(e));
+      } else {
+        pin->ptr = ptr;
+        pin->registered = true;
+      }
+      if (pin_ms) *pin_ms += wall_ms() - t0;
     }
-    pin->ptr = ptr;
-    pin->registered = true;
-    if (pin_ms) *pin_ms += wall_ms() - t0;
   }
   return PARALIA_OK;
 }
@@ -156,6 +169,8 @@ int Runtime::order_after_caller(const std::vector<int>& devs, const std::vector<
 int Runtime::ensure_device(int d) {
   if (d < 0 || d >= ndev_) return fail(PARALIA_ERR_INVALID_ARG, "GPU id %d out of range", d);
   DeviceCtx& c = devs_[d];
+  // the per-tile entry points may be called from several threads: one of them sets a GPU up
+  std::lock_guard<std::mutex> lk(device_mutex_);
   if (c.ready) return PARALIA_OK;
   PL_CUDA(cudaSetDevice(d));
   PL_CUDA(cudaStreamCreateWithFlags(&c.h2d, cudaStreamNonBlocking));

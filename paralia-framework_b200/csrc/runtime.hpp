@@ -111,6 +111,7 @@ class Runtime {
   bool peer_[PARALIA_MAX_UNITS][PARALIA_MAX_UNITS] = {};
   std::mutex call_mutex_;
   std::mutex init_mutex_;
+  std::mutex device_mutex_;
 };
 
 // RAII: remember the caller's current device and restore it on scope exit (the reference

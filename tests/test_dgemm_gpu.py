@@ -335,3 +335,21 @@ def test_executor_launches_what_the_plan_says(pl, orc, dims, T):
     items, grid = pl.plan_gemm(M, N, K, T, 1)
     assert rep.kernel_launches == len(items)
     assert (rep.grid_d1, rep.grid_d2) == grid
+
+
+def test_dgemm_operands_are_interleaved_views_of_one_parent(pl, orc):
+    """A and C are row ranges of ONE pageable parent matrix: their address ranges interleave
+    column by column, so page-locking the first makes the second start inside a registered
+    range that does not cover its end. The call must still succeed and be right."""
+    M, N, K = 300, 256, 256          # A is M x K, C is M x N, both cut out of a (2M) x 256 parent
+    parent = orc.matrix_f64(2 * M, 256, 77)
+    A = parent[:M, :]
+    C = parent[M:, :]
+    B = orc.matrix_f64(K, N, 43)
+    want = np.asfortranarray(C.copy())
+    orc.dgemm_tiled("N", "N", M, N, K, 1.0, np.asfortranarray(A), M, B, K, 0.5, want, M, 128)
+    pl.dgemm("N", "N", M, N, K, 1.0, A.ctypes.data, 2 * M, B, K, 0.5, C.ctypes.data, 2 * M,
+             locA=-1, locB=-1, locC=-1, ctl=pl.make_ctl(T=128, units=[0]))
+    assert orc.normwise_rel_err(C, want) <= tol(K)
+    # the rows of the parent that belong to A are untouched
+    assert np.array_equal(parent[:M, :], orc.matrix_f64(2 * M, 256, 77)[:M, :])

@@ -138,3 +138,20 @@ def test_dgemv_host_vs_openblas_golden(pl, orc, golden_dir):
         pl.dgemv(ta, M, N, alpha, A, M + pad, x, incx, beta, y, incy, ctl=pl.make_ctl(T=64, units=[0]))
         in_len = M if ta == "T" else N
         assert orc.normwise_rel_err(y[::incy], gold[f"dgemv_{i}"]) <= 8 * in_len * EPS64, case
+
+
+@pytest.mark.parametrize("ta", ["N", "T"])
+@pytest.mark.parametrize("beta", [0.0, 1e-20, 0.5, 1.0])
+def test_dgemv_empty_inner_dimension_scales_y(pl, ta, beta):
+    """No columns (op = N) or no rows (op = T) to multiply: y <- beta*y in one rounding, and
+    for beta == 0 y is set to zero without being read (a NaN in y must not survive), exactly
+    as BLAS defines it."""
+    n = 1001
+    y = np.linspace(-3.0, 7.0, n)
+    y[17] = np.nan if beta == 0.0 else 2.0 ** -600
+    want = np.zeros(n) if beta == 0.0 else beta * y
+    M, N = (n, 0) if ta == "N" else (0, n)
+    A = np.zeros((max(M, 1), max(N, 1)), order="F")
+    x = np.zeros(1)
+    pl.dgemv(ta, M, N, 1.25, A, max(M, 1), x, 1, beta, y, 1, ctl=pl.make_ctl(units=[0]))
+    assert np.array_equal(y, want)
