@@ -125,9 +125,11 @@ int PARALiA_group_dgemm(char TransA, char TransB, int64_t Mloc, int64_t Nloc, in
 
 // ------------------------------ per-tile kernels ------------------------------
 
-int PARALiA_tile_dgemm(int dev, void* stream, char TransA, char TransB, int64_t M, int64_t N,
-                       int64_t K, double alpha, const double* A, int64_t ldA, const double* B,
-                       int64_t ldB, double beta, double* C, int64_t ldC) {
+// `lone`: the launch has the GPU to itself (a caller's per-tile call); the calibration
+// benchmark passes 0 when it keeps several launches in flight, as the executor does.
+static int tile_dgemm_launch(int dev, void* stream, char TransA, char TransB, int64_t M, int64_t N,
+                             int64_t K, double alpha, const double* A, int64_t ldA, const double* B,
+                             int64_t ldB, double beta, double* C, int64_t ldC, int lone) {
   if (!valid_t(TransA) || !valid_t(TransB))
     return fail(PARALIA_ERR_INVALID_ARG, "transpose flag is not N or T");
   if (M < 0 || N < 0 || K < 0 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX)
@@ -164,8 +166,16 @@ int PARALiA_tile_dgemm(int dev, void* stream, char TransA, char TransB, int64_t 
   args.status = Runtime::get().dev(dev).status_dev;
   args.nparts = 1;
   args.parts[0].klen = (int32_t)K;
+  args.lone = lone;
   PL_CUDA(launch_dgemm_tile(mapA, mapB, args, ta != 0, tb == 0, s));
   return PARALIA_OK;
+}
+
+int PARALiA_tile_dgemm(int dev, void* stream, char TransA, char TransB, int64_t M, int64_t N,
+                       int64_t K, double alpha, const double* A, int64_t ldA, const double* B,
+                       int64_t ldB, double beta, double* C, int64_t ldC) {
+  // a per-tile call: nothing of this library runs beside it
+  return tile_dgemm_launch(dev, stream, TransA, TransB, M, N, K, alpha, A, ldA, B, ldB, beta, C, ldC, 1);
 }
 
 int PARALiA_tile_status(int dev) {
@@ -593,15 +603,16 @@ int PARALiA_bench_tile_dgemm_chain(int dev, char TransA, char TransB, int64_t T,
   int rc = PARALIA_OK;
   const int64_t lda = norm_t(TransA) ? Kc : T, ldb = norm_t(TransB) ? T : Kc;
   for (int i = 0; i < 2 && rc == PARALIA_OK; ++i)
-    rc = PARALiA_tile_dgemm(dev, dc.exec[0], TransA, TransB, T, T, Kc, 1.0, A, lda, B, ldb, 0.5, C, T);
+    rc = tile_dgemm_launch(dev, dc.exec[0], TransA, TransB, T, T, Kc, 1.0, A, lda, B, ldb, 0.5, C, T,
+                           reps == 1);
   if (rc == PARALIA_OK) {
     PL_CUDA(cudaSetDevice(dev));
     PL_CUDA(cudaDeviceSynchronize());
     PL_CUDA(cudaEventRecord(e0, dc.exec[0]));
     for (int s = 1; s < S; ++s) PL_CUDA(cudaStreamWaitEvent(dc.exec[s], e0, 0));
     for (int i = 0; i < reps && rc == PARALIA_OK; ++i)
-      rc = PARALiA_tile_dgemm(dev, dc.exec[i % S], TransA, TransB, T, T, Kc, 1.0, A, lda, B, ldb, 0.5,
-                              C + (size_t)(i % S) * n, T);
+      rc = tile_dgemm_launch(dev, dc.exec[i % S], TransA, TransB, T, T, Kc, 1.0, A, lda, B, ldb, 0.5,
+                             C + (size_t)(i % S) * n, T, reps == 1);
     PL_CUDA(cudaSetDevice(dev));
     for (int s = 1; s < S; ++s) {
       PL_CUDA(cudaEventRecord(join[s], dc.exec[s]));

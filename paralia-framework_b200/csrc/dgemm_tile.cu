@@ -6,24 +6,26 @@
 // the parameter block built at Library_scheduler/src/Functions/dgemm.cpp:181-197.
 //
 // Blackwell's tcgen05 tensor path has no FP64 kind, so the FP64 tensor cores are driven
-// with warp-level mma.sync (DMMA). The kernel is persistent: one CTA (288 threads) per SM
-// walks a static list of work items of the launch's C tile, so that the producer already
-// fills the pipeline of the next item while the consumers write the previous one back.
+// with warp-level mma.sync (DMMA). One CTA (288 threads) computes one work item:
 //   * warp 8 is the producer: one lane issues TMA 3-D tiled loads (128-byte swizzle, no
-//     multicast) for a slice of A and a slice of B per 16-deep k stage into a 6-stage ring,
-//     completion signalled on "full" mbarriers;
+//     multicast) for a 128 x 16 slice of A and a 16 x 128 slice of B per stage into a
+//     6-stage ring, completion signalled on "full" mbarriers;
 //   * warps 0-7 are consumers: each owns a piece of the item's C tile, reads operand
 //     fragments from the swizzled stage with conflict-free 64-bit loads and issues m16n8k8
 //     DMMA; a warp releases the stage on an "empty" mbarrier;
 //   * the epilogue applies alpha/beta from registers straight to C.
+// The grid is the list of work items and the hardware hands them to the SMs as they become
+// free. (A persistent CTA per SM walking a fixed list, or drawing items from a counter, was
+// measured slower, alone and with several launches in flight.)
 //
-// Work items. The launch's C tile is cut into 128 x 128 CTA tiles. Those that fill whole
-// rounds of the grid are "full" items (each consumer warp owns 64 (m) x 32 (n)). What is
-// left after the last whole round would leave most SMs idle for the time of a full item, so
-// those CTA tiles are cut into four 64 x 64 "quarter" items (each warp owns 32 x 16) and
-// dealt out again, unless that takes as many rounds as the full items would. Item i goes to
-// CTA i mod gridDim.x. Every element of C sees its k values in the same order in either
-// item shape, so the split never changes a result bit.
+// Work items. The launch's C tile is cut into 128 x 128 CTA tiles, one item each (a consumer
+// warp owns 64 (m) x 32 (n)). A launch that has the GPU to itself (a per-tile call, the last
+// tiles of a problem) would leave most SMs idle during its last partial round of CTA tiles;
+// such a launch cuts the CTA tiles of that round into four 64 x 64 "quarter" items (a warp
+// owns 32 x 16, a second launch of the kernel on the same stream), unless they would take as
+// many rounds again. A quarter item loads the same stages as its parent tile and multiplies
+// one quadrant of them. Every element of C sees its
+// k values in the same order in either item shape, so the split never changes a result bit.
 //
 // Mapping onto the MMA: the instruction computes D[i][j] += sum_k P[i][k] Q[k][j] where a
 // thread ends up holding two j-adjacent values. C is column-major, so j is bound to the
@@ -56,8 +58,8 @@ __device__ __forceinline__ int kperm(int q, int t) {
   return 8 * (t >> 1) + 2 * ((t + q) & 3) + (t & 1);
 }
 
-// Byte offset, inside an operand slice, of element (row = 16*blk + 8*h + g, k), without the
-// 2048-byte-per-16-rows block term.
+// Byte offset, inside a 128-row operand slice, of element (row = 16*blk + 8*h + g, k),
+// without the 2048-byte-per-16-rows block term.
 template <bool KC>
 __device__ __forceinline__ uint32_t lane_off(int g, int h, int k) {
   if (KC) {
@@ -74,95 +76,71 @@ __device__ __forceinline__ double lds64(const unsigned char* base, uint32_t off)
   return *reinterpret_cast<const double*>(base + off);
 }
 
-// One work item of a CTA: origin of its piece of C and whether it is a quarter item.
+// One work item: origin of the CTA tile whose operand slices are loaded, quadrant of it that
+// is computed (quarter items), origin of the item's piece of C.
 struct Item {
+  int tm0, tn0;
+  int qm, qn;
   int m0, n0;
   bool quarter;
   bool valid;
 };
 
-__device__ __forceinline__ Item decode_item(const DgemmArgs& args, int item) {
+// Full items and quarter items run as two launches of the kernel (QUARTER = false / true):
+// block b of the first is CTA tile b, block b of the second is quadrant b mod 4 of CTA tile
+// full_items + b / 4.
+template <bool QUARTER>
+__device__ __forceinline__ Item decode_item(const DgemmArgs& args, int block) {
   Item w;
-  int tile, quad = 0;
-  w.quarter = item >= args.full_items;
-  if (w.quarter) {
-    const int q = item - args.full_items;
-    tile = args.full_items + (q >> 2);
-    quad = q & 3;
-  } else {
-    tile = item;
-  }
+  w.quarter = QUARTER;
+  const int tile = QUARTER ? args.full_items + (block >> 2) : block;
+  const int quad = QUARTER ? (block & 3) : 0;
   // CTA tiles are numbered down the columns of C: consecutive CTAs share a slice of B
   const int tm = tile % args.tiles_m, tn = tile / args.tiles_m;
-  w.m0 = tm * DG_BM + (quad & 1) * (DG_BM / 2);
-  w.n0 = tn * DG_BN + (quad >> 1) * (DG_BN / 2);
+  w.qm = quad & 1;
+  w.qn = quad >> 1;
+  w.tm0 = tm * DG_BM;
+  w.tn0 = tn * DG_BN;
+  w.m0 = w.tm0 + w.qm * (DG_BM / 2);
+  w.n0 = w.tn0 + w.qn * (DG_BN / 2);
   w.valid = w.m0 < args.M && w.n0 < args.N;
   return w;
 }
 
-// Rows of A and of B that one stage of an item brings in.
+// Warp tile of the two item shapes: JB groups of 8 rows (m), IB groups of 16 columns (n).
 template <bool QUARTER>
 struct Shape {
-  static constexpr int ROWS_A = QUARTER ? DG_BM / 2 : DG_BM;
-  static constexpr int ROWS_B = QUARTER ? DG_BN / 2 : DG_BN;
-  static constexpr uint32_t STAGE_TX = (ROWS_A + ROWS_B) * DG_BK * 8;
-  static constexpr int JB = QUARTER ? 4 : 8;   // 8-row (m) groups per consumer warp
-  static constexpr int IB = QUARTER ? 1 : 2;   // 16-column (n) groups per consumer warp
+  static constexpr int JB = QUARTER ? 4 : 8;
+  static constexpr int IB = QUARTER ? 1 : 2;
 };
 
-// The B slice of a stage always starts behind room for a full A slice.
-constexpr uint32_t DG_B_OFFSET = DG_BM * DG_BK * 8;
-
+// Main loop and epilogue of one item for one consumer warp. Returns false if a wait gave up.
 template <bool A_KC, bool B_KC, bool QUARTER>
-__device__ __forceinline__ void produce_stage(unsigned char* sA, const CUtensorMap* mapA,
-                                              const CUtensorMap* mapB, uint64_t* bar,
-                                              const DgemmKPart& part, int kk, int m0, int n0) {
+__device__ __forceinline__ bool consume_item(const DgemmArgs& args, const Item& w,
+                                             const unsigned char* smem, uint64_t* full_bar,
+                                             uint64_t* empty_bar, volatile int* abort_flag,
+                                             int warp, int lane) {
   using S = Shape<QUARTER>;
-  unsigned char* sB = sA + DG_B_OFFSET;
-  mbar_expect_tx(bar, S::STAGE_TX);
-  if (A_KC) {
-    // k-contiguous operand: boxes of 64 rows x 16 k
-#pragma unroll
-    for (int c = 0; c < S::ROWS_A / 64; ++c)
-      tma_load_3d(sA + c * 8192, mapA, bar, part.a_k + kk, part.a_m + m0 + c * 64, part.a_z);
-  } else {
-    // row-contiguous operand: boxes of 16 rows x 16 k
-#pragma unroll
-    for (int c = 0; c < S::ROWS_A / 16; ++c)
-      tma_load_3d(sA + c * 2048, mapA, bar, part.a_m + m0 + c * 16, part.a_k + kk, part.a_z);
-  }
-  if (B_KC) {
-#pragma unroll
-    for (int c = 0; c < S::ROWS_B / 64; ++c)
-      tma_load_3d(sB + c * 8192, mapB, bar, part.b_k + kk, part.b_n + n0 + c * 64, part.b_z);
-  } else {
-#pragma unroll
-    for (int c = 0; c < S::ROWS_B / 16; ++c)
-      tma_load_3d(sB + c * 2048, mapB, bar, part.b_n + n0 + c * 16, part.b_k + kk, part.b_z);
-  }
-}
-
-// Main loop of one item for one consumer warp. Returns false if a wait gave up.
-template <bool A_KC, bool B_KC, bool QUARTER>
-__device__ __forceinline__ bool consume_item(double (&acc)[2][8][4], const unsigned char* smem,
-                                             uint64_t* full_bar, uint64_t* empty_bar,
-                                             volatile int* abort_flag, int* status, int& it,
-                                             int stages, int warp, int lane) {
-  using S = Shape<QUARTER>;
-  const int g = lane >> 2, t = lane & 3;
+  const int g = lane >> 2;
+  const int t = lane & 3;
   const int wn = warp & 3;   // column slice of the item
   const int wm = warp >> 2;  // row slice of the item
-  // Per-lane byte offsets for the four k steps of a stage and the two 8-row halves.
+
+  // Per-lane byte offsets for the four k steps of a stage and the two 8-row halves. A slice
+  // is made of 16-row blocks of 2048 bytes; a quarter item works on one half of each slice.
   uint32_t offP[4][2], offQ[4][2];
 #pragma unroll
   for (int q = 0; q < 4; ++q) {
     const int k = kperm(q, t);
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-      offP[q][h] = lane_off<B_KC>(g, h, k) + (uint32_t)(wn * S::IB * 2048) + DG_B_OFFSET;
-      offQ[q][h] = lane_off<A_KC>(g, h, k) + (uint32_t)(wm * (S::JB / 2) * 2048);
+      offP[q][h] = lane_off<B_KC>(g, h, k) + (uint32_t)((w.qn * 4 + wn * S::IB) * 2048) +
+                   (uint32_t)(DG_BM * DG_BK * 8);
+      offQ[q][h] = lane_off<A_KC>(g, h, k) + (uint32_t)((w.qm * 4 + wm * (S::JB / 2)) * 2048);
     }
   }
+
+  double acc[S::IB][S::JB][4];
 #pragma unroll
   for (int ib = 0; ib < S::IB; ++ib)
 #pragma unroll
@@ -170,13 +148,16 @@ __device__ __forceinline__ bool consume_item(double (&acc)[2][8][4], const unsig
 #pragma unroll
       for (int r = 0; r < 4; ++r) acc[ib][jb][r] = 0.0;
 
-  for (int ks = 0; ks < stages; ++ks, ++it) {
+  int total = 0;
+  for (int p = 0; p < args.nparts; ++p) total += (args.parts[p].klen + DG_BK - 1) / DG_BK;
+
+  for (int it = 0; it < total; ++it) {
     const int s = it % DG_STAGES;
     const uint32_t par = (uint32_t)((it / DG_STAGES) & 1);
     if (!mbar_wait_bounded(&full_bar[s], par, abort_flag)) {
       if (!*abort_flag) {
         *abort_flag = 1;
-        atomicExch(status, KERR_FULL_WAIT_TIMEOUT);
+        atomicExch(args.status, KERR_FULL_WAIT_TIMEOUT);
       }
       return false;
     }
@@ -202,15 +183,8 @@ __device__ __forceinline__ bool consume_item(double (&acc)[2][8][4], const unsig
     __syncwarp();
     if (lane == 0) mbar_arrive(&empty_bar[s]);
   }
-  return true;
-}
 
-template <bool QUARTER>
-__device__ __forceinline__ void epilogue(const double (&acc)[2][8][4], const DgemmArgs& args,
-                                         int m0, int n0, int warp, int lane) {
-  using S = Shape<QUARTER>;
-  const int g = lane >> 2, t = lane & 3;
-  const int wn = warp & 3, wm = warp >> 2;
+  // -------------------------------- epilogue --------------------------------
   const double alpha = args.alpha, beta_c = args.beta_c, beta_src = args.beta_src;
   const bool use_c = beta_c != 0.0;
   const bool use_src = (args.Csrc != nullptr) && beta_src != 0.0;
@@ -218,13 +192,13 @@ __device__ __forceinline__ void epilogue(const double (&acc)[2][8][4], const Dge
   for (int ib = 0; ib < S::IB; ++ib) {
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
-      const int n = n0 + wn * (S::IB * 16) + ib * 16 + hh * 8 + g;
+      const int n = w.n0 + wn * (S::IB * 16) + ib * 16 + hh * 8 + g;
       if (n >= args.N) continue;
       double* crow = args.C + (int64_t)n * args.ldc;
       const double* srow = use_src ? args.Csrc + (int64_t)n * args.ldcsrc : nullptr;
 #pragma unroll
       for (int jb = 0; jb < S::JB; ++jb) {
-        const int m = m0 + wm * (S::JB * 8) + jb * 8 + 2 * t;
+        const int m = w.m0 + wm * (S::JB * 8) + jb * 8 + 2 * t;
         if (m >= args.M) continue;
         double v0 = alpha * acc[ib][jb][2 * hh];
         double v1 = alpha * acc[ib][jb][2 * hh + 1];
@@ -253,9 +227,10 @@ __device__ __forceinline__ void epilogue(const double (&acc)[2][8][4], const Dge
       }
     }
   }
+  return true;
 }
 
-template <bool A_KC, bool B_KC>
+template <bool A_KC, bool B_KC, bool QUARTER>
 __global__ void __launch_bounds__(DG_THREADS, 1)
 dgemm_tile_kernel(const __grid_constant__ CUtensorMap mapA,
                   const __grid_constant__ CUtensorMap mapB,
@@ -270,6 +245,8 @@ dgemm_tile_kernel(const __grid_constant__ CUtensorMap mapA,
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const Item w = decode_item<QUARTER>(args, (int)blockIdx.x);
+  if (!w.valid) return;   // a quadrant outside an edge tile: the whole CTA leaves
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < DG_STAGES; ++s) {
@@ -281,44 +258,48 @@ dgemm_tile_kernel(const __grid_constant__ CUtensorMap mapA,
   }
   __syncthreads();
 
-  const int total_items = args.full_items + args.quarter_items;
-  // 16-deep stages of one item (the same for every item of the launch)
-  int stages = 0;
-  for (int p = 0; p < args.nparts; ++p) stages += (args.parts[p].klen + DG_BK - 1) / DG_BK;
-
-  if (warp >= DG_CONSUMER_WARPS) {
+  if (warp == DG_CONSUMER_WARPS) {
     // ------------------------------ producer ------------------------------
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(DG_REGS_PRODUCER));
-    if (warp == DG_CONSUMER_WARPS && lane == 0) {
+    if (lane == 0) {
       if (args.nparts > 0) {
         prefetch_tensormap(&mapA);
         prefetch_tensormap(&mapB);
       }
       int it = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-        const Item w = decode_item(args, item);
-        if (!w.valid) continue;
-        for (int p = 0; p < args.nparts && ok; ++p) {
-          const DgemmKPart part = args.parts[p];
-          for (int kk = 0; kk < part.klen; kk += DG_BK, ++it) {
-            const int s = it % DG_STAGES;
-            if (it >= DG_STAGES) {
-              const uint32_t par = (uint32_t)(((it / DG_STAGES) - 1) & 1);
-              if (!mbar_wait_bounded(&empty_bar[s], par, abort_flag)) {
-                if (!*abort_flag) {
-                  *abort_flag = 1;
-                  atomicExch(args.status, KERR_EMPTY_WAIT_TIMEOUT);
-                }
-                ok = false;
-                break;
+      for (int p = 0; p < args.nparts && ok; ++p) {
+        const DgemmKPart part = args.parts[p];
+        for (int kk = 0; kk < part.klen; kk += DG_BK, ++it) {
+          const int s = it % DG_STAGES;
+          if (it >= DG_STAGES) {
+            const uint32_t par = (uint32_t)(((it / DG_STAGES) - 1) & 1);
+            if (!mbar_wait_bounded(&empty_bar[s], par, abort_flag)) {
+              if (!*abort_flag) {
+                *abort_flag = 1;
+                atomicExch(args.status, KERR_EMPTY_WAIT_TIMEOUT);
               }
+              ok = false;
+              break;
             }
-            unsigned char* sA = smem + s * DG_STAGE_BYTES;
-            if (w.quarter)
-              produce_stage<A_KC, B_KC, true>(sA, &mapA, &mapB, &full_bar[s], part, kk, w.m0, w.n0);
-            else
-              produce_stage<A_KC, B_KC, false>(sA, &mapA, &mapB, &full_bar[s], part, kk, w.m0, w.n0);
+          }
+          unsigned char* sA = smem + s * DG_STAGE_BYTES;
+          unsigned char* sB = sA + DG_BM * DG_BK * 8;
+          mbar_expect_tx(&full_bar[s], DG_STAGE_BYTES);
+          if (A_KC) {
+            tma_load_3d(sA, &mapA, &full_bar[s], part.a_k + kk, part.a_m + w.tm0, part.a_z);
+          } else {
+#pragma unroll
+            for (int c = 0; c < DG_BM / 16; ++c)
+              tma_load_3d(sA + c * 2048, &mapA, &full_bar[s], part.a_m + w.tm0 + c * 16,
+                          part.a_k + kk, part.a_z);
+          }
+          if (B_KC) {
+            tma_load_3d(sB, &mapB, &full_bar[s], part.b_k + kk, part.b_n + w.tn0, part.b_z);
+          } else {
+#pragma unroll
+            for (int c = 0; c < DG_BN / 16; ++c)
+              tma_load_3d(sB + c * 2048, &mapB, &full_bar[s], part.b_n + w.tn0 + c * 16,
+                          part.b_k + kk, part.b_z);
           }
         }
       }
@@ -338,24 +319,7 @@ dgemm_tile_kernel(const __grid_constant__ CUtensorMap mapA,
   }
 
   // -------------------------------- consumers --------------------------------
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(DG_REGS_CONSUMER));
-  double acc[2][8][4];
-  int it = 0;
-  for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
-    const Item w = decode_item(args, item);
-    if (!w.valid) continue;
-    if (w.quarter) {
-      if (!consume_item<A_KC, B_KC, true>(acc, smem, full_bar, empty_bar, abort_flag, args.status,
-                                          it, stages, warp, lane))
-        return;
-      epilogue<true>(acc, args, w.m0, w.n0, warp, lane);
-    } else {
-      if (!consume_item<A_KC, B_KC, false>(acc, smem, full_bar, empty_bar, abort_flag, args.status,
-                                           it, stages, warp, lane))
-        return;
-      epilogue<false>(acc, args, w.m0, w.n0, warp, lane);
-    }
-  }
+  consume_item<A_KC, B_KC, QUARTER>(args, w, smem, full_bar, empty_bar, abort_flag, warp, lane);
 }
 
 // ------------------------------------------------------------------------------
@@ -465,7 +429,10 @@ __global__ void bounded_wait_selftest_kernel(int* status, long long budget_clock
   }
 }
 
-// SMs of the current device (one persistent CTA per SM).
+}  // namespace
+
+namespace {
+// SMs of the current device.
 int current_sm_count() {
   static int cached[64] = {};
   int dev = 0;
@@ -480,28 +447,26 @@ int current_sm_count() {
   }
   return cached[dev];
 }
-
 }  // namespace
 
-void dgemm_tile_schedule(int M, int N, int sms, int* tiles_m, int* full_items, int* quarter_items,
-                         int* grid) {
+void dgemm_tile_schedule(int M, int N, int sms, bool lone, int* tiles_m, int* full_items,
+                         int* quarter_items) {
   const int tm = (M + DG_BM - 1) / DG_BM, tn = (N + DG_BN - 1) / DG_BN;
   const int tiles = tm * tn;
   const int G = sms > 0 ? sms : 1;
-  int full = (tiles / G) * G;
-  const int rest = tiles - full;
-  int quarters = 0;
-  if (rest > 0) {
+  int full = tiles, quarters = 0;
+  const int rest = tiles % G;
+  if (lone && rest > 0) {
     // quarter items pay off only if they take fewer rounds than four quarters' worth
     const int rounds = (4 * rest + G - 1) / G;
-    if (rounds < 4) quarters = 4 * rest;
-    else full += rest;
+    if (rounds < 4) {
+      full = tiles - rest;
+      quarters = 4 * rest;
+    }
   }
   *tiles_m = tm;
   *full_items = full;
   *quarter_items = quarters;
-  const int items = full + quarters;
-  *grid = items < G ? items : G;
 }
 
 cudaError_t launch_bounded_wait_selftest(int* status, long long budget_clocks, cudaStream_t stream) {
@@ -509,19 +474,35 @@ cudaError_t launch_bounded_wait_selftest(int* status, long long budget_clocks, c
   return cudaGetLastError();
 }
 
+namespace {
+template <bool A_KC, bool B_KC>
+cudaError_t configure_pair() {
+  cudaError_t e = cudaFuncSetAttribute(dgemm_tile_kernel<A_KC, B_KC, false>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, DG_SMEM_BYTES);
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(dgemm_tile_kernel<A_KC, B_KC, true>,
+                              cudaFuncAttributeMaxDynamicSharedMemorySize, DG_SMEM_BYTES);
+}
+
+template <bool A_KC, bool B_KC>
+cudaError_t launch_pair(const CUtensorMap& mapA, const CUtensorMap& mapB, const DgemmArgs& args,
+                        cudaStream_t stream) {
+  const dim3 block(DG_THREADS);
+  if (args.full_items > 0)
+    dgemm_tile_kernel<A_KC, B_KC, false><<<dim3(args.full_items), block, DG_SMEM_BYTES, stream>>>(
+        mapA, mapB, args);
+  if (args.quarter_items > 0)
+    dgemm_tile_kernel<A_KC, B_KC, true><<<dim3(args.quarter_items), block, DG_SMEM_BYTES, stream>>>(
+        mapA, mapB, args);
+  return cudaGetLastError();
+}
+}  // namespace
+
 cudaError_t dgemm_tile_configure() {
-  cudaError_t e;
-  e = cudaFuncSetAttribute(dgemm_tile_kernel<false, false>,
-                           cudaFuncAttributeMaxDynamicSharedMemorySize, DG_SMEM_BYTES);
-  if (e != cudaSuccess) return e;
-  e = cudaFuncSetAttribute(dgemm_tile_kernel<false, true>,
-                           cudaFuncAttributeMaxDynamicSharedMemorySize, DG_SMEM_BYTES);
-  if (e != cudaSuccess) return e;
-  e = cudaFuncSetAttribute(dgemm_tile_kernel<true, false>,
-                           cudaFuncAttributeMaxDynamicSharedMemorySize, DG_SMEM_BYTES);
-  if (e != cudaSuccess) return e;
-  e = cudaFuncSetAttribute(dgemm_tile_kernel<true, true>,
-                           cudaFuncAttributeMaxDynamicSharedMemorySize, DG_SMEM_BYTES);
+  cudaError_t e = configure_pair<false, false>();
+  if (e == cudaSuccess) e = configure_pair<false, true>();
+  if (e == cudaSuccess) e = configure_pair<true, false>();
+  if (e == cudaSuccess) e = configure_pair<true, true>();
   return e;
 }
 
@@ -529,24 +510,14 @@ cudaError_t launch_dgemm_tile(const CUtensorMap& mapA, const CUtensorMap& mapB,
                               const DgemmArgs& args_in, bool a_kcontig, bool b_kcontig,
                               cudaStream_t stream) {
   DgemmArgs args = args_in;
-  int grid_x = 0;
-  dgemm_tile_schedule(args.M, args.N, current_sm_count(), &args.tiles_m, &args.full_items,
-                      &args.quarter_items, &grid_x);
-  if (grid_x <= 0) return cudaSuccess;
-  dim3 grid(grid_x);
-  dim3 block(DG_THREADS);
-  if (a_kcontig) {
-    if (b_kcontig)
-      dgemm_tile_kernel<true, true><<<grid, block, DG_SMEM_BYTES, stream>>>(mapA, mapB, args);
-    else
-      dgemm_tile_kernel<true, false><<<grid, block, DG_SMEM_BYTES, stream>>>(mapA, mapB, args);
-  } else {
-    if (b_kcontig)
-      dgemm_tile_kernel<false, true><<<grid, block, DG_SMEM_BYTES, stream>>>(mapA, mapB, args);
-    else
-      dgemm_tile_kernel<false, false><<<grid, block, DG_SMEM_BYTES, stream>>>(mapA, mapB, args);
-  }
-  return cudaGetLastError();
+  dgemm_tile_schedule(args.M, args.N, current_sm_count(), args.lone != 0, &args.tiles_m,
+                      &args.full_items, &args.quarter_items);
+  if (args.full_items + args.quarter_items <= 0) return cudaSuccess;
+  if (a_kcontig)
+    return b_kcontig ? launch_pair<true, true>(mapA, mapB, args, stream)
+                     : launch_pair<true, false>(mapA, mapB, args, stream);
+  return b_kcontig ? launch_pair<false, true>(mapA, mapB, args, stream)
+                   : launch_pair<false, false>(mapA, mapB, args, stream);
 }
 
 cudaError_t launch_dgemm_generic(char ta, char tb, int M, int N, int K, double alpha,

@@ -12,12 +12,7 @@ constexpr int DG_BN = 128;      // columns of C per CTA
 constexpr int DG_BK = 16;       // k per pipeline stage (16 doubles = one 128-byte swizzle row)
 constexpr int DG_STAGES = 6;    // 6 x 32 KB of operand tiles in flight
 constexpr int DG_CONSUMER_WARPS = 8;
-// Two consumer warp groups (8 warps) and one producer warp group of which one lane works:
-// whole groups of four warps so that the register file can be re-divided between them
-// (setmaxnreg): the consumers take 232 registers per thread, the producer group keeps 40.
-constexpr int DG_THREADS = (DG_CONSUMER_WARPS + 4) * 32;
-constexpr int DG_REGS_CONSUMER = 232;
-constexpr int DG_REGS_PRODUCER = 40;
+constexpr int DG_THREADS = (DG_CONSUMER_WARPS + 1) * 32;  // + one TMA producer warp
 constexpr int DG_STAGE_BYTES = (DG_BM + DG_BN) * DG_BK * 8;
 constexpr int DG_SMEM_BYTES = DG_STAGES * DG_STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 constexpr int DG_MAX_PARTS = 64;
@@ -40,6 +35,8 @@ struct DgemmArgs {
   int32_t nparts;
   int32_t vec_ok;       // C and Csrc allow 16-byte accesses
   int* status;          // device word that receives a KERR_* code on a timed-out wait
+  int32_t lone;         // the launch is expected to have the GPU to itself: its last partial
+                        // round of CTA tiles is cut into quarter items
   // Work items of the launch, filled in by launch_dgemm_tile (dgemm_tile_schedule):
   // items [0, full_items) are 128 x 128 CTA tiles, the next quarter_items are 64 x 64
   // quarters of the CTA tiles that follow; tiles_m = CTA tiles per column of C.
@@ -47,14 +44,14 @@ struct DgemmArgs {
   DgemmKPart parts[DG_MAX_PARTS];
 };
 
-// The static work list of a launch over an M x N C tile on a GPU with `sms` SMs: how many
-// CTA tiles are whole items, how many quarter items follow, and the grid size.
-void dgemm_tile_schedule(int M, int N, int sms, int* tiles_m, int* full_items, int* quarter_items,
-                         int* grid);
+// The work list of a launch over an M x N C tile on a GPU with `sms` SMs: how many CTA tiles
+// are whole items and how many quarter items follow. The grid is their sum.
+void dgemm_tile_schedule(int M, int N, int sms, bool lone, int* tiles_m, int* full_items,
+                         int* quarter_items);
 
-// Rows per TMA box of an operand stored with k contiguous (box = 16 k x DG_KC_BOX_ROWS rows);
-// an operand stored row-contiguous uses boxes of 16 rows x 16 k.
-constexpr int DG_KC_BOX_ROWS = 64;
+// Rows per TMA box of an operand stored with k contiguous (box = 16 k x 128 rows); an
+// operand stored row-contiguous uses boxes of 16 rows x 16 k.
+constexpr int DG_KC_BOX_ROWS = 128;
 
 // Launch on `stream`. a_kcontig: A is stored with k contiguous (TransA == 'T' for a
 // column-major A); b_kcontig: B is stored with k contiguous (TransB == 'N').

@@ -555,7 +555,7 @@ template <> struct TileKernel<float> { using Args = SgemmArgs; };
 
 // Enqueue subkernels [ki0, ki1) of C tile `ct` on unit ui as one launch.
 template <typename T>
-int enqueue_subkernels(GemmCall<T>& g, int ui, int order_idx, int ct, int ki0, int ki1) {
+int enqueue_subkernels(GemmCall<T>& g, int ui, int order_idx, int ct, int ki0, int ki1, int band) {
   constexpr bool IS_F64 = std::is_same<T, double>::value;
   Runtime& rt = Runtime::get();
   UnitState& u = g.units[ui];
@@ -609,6 +609,8 @@ int enqueue_subkernels(GemmCall<T>& g, int ui, int order_idx, int ct, int ki0, i
   }
   args.M = (int32_t)g.mrows(mi);
   args.N = (int32_t)g.ncols(ni);
+  // launches of a band of one or two C tiles have the GPU nearly to themselves
+  if constexpr (IS_F64) args.lone = band <= 2 ? 1 : 0;
   args.alpha = g.alpha;
   args.status = dc.status_dev;
   args.Csrc = nullptr;
@@ -720,7 +722,12 @@ void build_items(const GemmCall<T>& g, UnitState& u, const GemmModelInput& model
   const BandHints hints = band_hints(model_in, g.Tt, u.dev, pulling, a_sharers, b_sharers, row_len);
   std::vector<int> bands;
   plan_band_sizes((int)u.ctiles.size(), (int)g.Kt, g.evict, hints, &bands);
-  plan_launch_order(bands, (int)g.Kt, g.evict, DG_MAX_PARTS, &u.items);
+  // FP32 launches take one k tile each: the tcgen05 kernel streams its packed operand strips
+  // through L2 with all CTAs of a launch in step, and they drift apart over longer k loops
+  // (measured on a device-resident 40960^3: one k tile per launch 224 TFLOP/s, two 210,
+  // four 189). PARALIA_KCHAIN still overrides.
+  const int max_chain = std::is_same<T, float>::value && plan_kchain_forced() == 0 ? 1 : DG_MAX_PARTS;
+  plan_launch_order(bands, (int)g.Kt, g.evict, max_chain, &u.items);
   u.cursor = 0;
 }
 
@@ -761,15 +768,26 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
 
   double pin_ms = 0.0;
   int rc = PARALIA_OK;
+  // a column-major matrix spans ld*(cols-1) + rows elements, not ld*cols
+  const size_t spanA = K > 0 ? matrix_span_bytes(g.A.ld, g.A.rows, g.A.cols, g.esz) : 0;
+  const size_t spanB = K > 0 ? matrix_span_bytes(g.B.ld, g.B.rows, g.B.cols, g.esz) : 0;
+  const size_t spanC = matrix_span_bytes(g.C.ld, M, N, g.esz);
   if (K > 0) {
-    // a column-major matrix spans ld*(cols-1) + rows elements, not ld*cols
-    rc = resolve_operand(&g.A, locA, matrix_span_bytes(g.A.ld, g.A.rows, g.A.cols, g.esz), ngpu, &pin_ms);
-    if (rc == PARALIA_OK)
-      rc = resolve_operand(&g.B, locB, matrix_span_bytes(g.B.ld, g.B.rows, g.B.cols, g.esz), ngpu, &pin_ms);
+    rc = resolve_operand_location(g.A.ptr, locA, spanA, ngpu, &g.A.loc, nullptr, nullptr);
+    if (rc == PARALIA_OK) rc = resolve_operand_location(g.B.ptr, locB, spanB, ngpu, &g.B.loc, nullptr, nullptr);
   } else {
     g.A.loc = g.B.loc = -1;
   }
-  if (rc == PARALIA_OK) rc = resolve_operand(&g.C, locC, matrix_span_bytes(g.C.ld, M, N, g.esz), ngpu, &pin_ms);
+  if (rc == PARALIA_OK) rc = resolve_operand_location(g.C.ptr, locC, spanC, ngpu, &g.C.loc, nullptr, nullptr);
+  if (rc == PARALIA_OK) {
+    // host operands are page-locked together: views of one parent matrix overlap
+    HostRange hr[3] = {{g.A.loc == -1 && K > 0 ? g.A.ptr : nullptr, spanA},
+                       {g.B.loc == -1 && K > 0 ? g.B.ptr : nullptr, spanB},
+                       {g.C.loc == -1 ? g.C.ptr : nullptr, spanC}};
+    HostPin pins[3];
+    rc = pin_host_ranges(hr, 3, pins, &pin_ms);
+    g.A.pin = pins[0]; g.B.pin = pins[1]; g.C.pin = pins[2];
+  }
   const bool keep_pinned = ctl && (ctl->flags & PARALIA_FLAG_KEEP_PINNED);
   auto cleanup_pins = [&]() {
     if (!keep_pinned) { unpin(&g.A); unpin(&g.B); unpin(&g.C); }
@@ -1057,7 +1075,7 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
       if (u.cursor >= u.items.size()) continue;
       const UnitState::Item item = u.items[u.cursor++];
       rc = enqueue_subkernels<T>(g, ui, item.order_idx, u.ctiles[item.order_idx], item.ki0,
-                                 item.ki1);
+                                 item.ki1, item.band);
       if (rc != PARALIA_OK) break;
       if (u.cursor < u.items.size()) work_left = true;
     }

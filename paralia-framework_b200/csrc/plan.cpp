@@ -5,11 +5,16 @@
 
 namespace paralia {
 
-int plan_kchain_len(bool bounded_cache, int ki0, int max_parts) {
+int plan_kchain_forced() {
   static const int forced = [] {
     const char* e = getenv("PARALIA_KCHAIN");
     return e ? atoi(e) : 0;
   }();
+  return forced;
+}
+
+int plan_kchain_len(bool bounded_cache, int ki0, int max_parts) {
+  const int forced = plan_kchain_forced();
   int len = bounded_cache ? 1 : (forced > 0 ? forced : (ki0 == 0 ? 1 : 4));
   len = std::min(len, max_parts);
   return std::max(len, 1);
@@ -92,13 +97,13 @@ void plan_launch_order(const std::vector<int>& bands, int Kt, bool bounded_cache
   for (int band : bands) {
     const int b1 = b0 + band;
     if (Kt == 0) {   // no product: one launch per tile scales C by beta
-      for (int oi = b0; oi < b1; ++oi) items->push_back({oi, 0, 0});
+      for (int oi = b0; oi < b1; ++oi) items->push_back({oi, 0, 0, band});
       b0 = b1;
       continue;
     }
     for (int ki0 = 0; ki0 < kt;) {
       const int ki1 = std::min(kt, ki0 + plan_kchain_len(bounded_cache, ki0, max_parts));
-      for (int oi = b0; oi < b1; ++oi) items->push_back({oi, ki0, ki1});
+      for (int oi = b0; oi < b1; ++oi) items->push_back({oi, ki0, ki1, band});
       ki0 = ki1;
     }
     b0 = b1;

@@ -14,7 +14,11 @@ namespace paralia {
 // over the k tiles [ki0, ki1).
 struct LaunchItem {
   int order_idx, ki0, ki1;
+  int band;   // number of C tiles in the band the launch belongs to
 };
+
+// Value of PARALIA_KCHAIN (0 = not set).
+int plan_kchain_forced();
 
 // How many consecutive k tiles the launch starting at k tile ki0 covers. A function of
 // ki0 and the cache mode only (never of the tile, the unit or the GPU count): the first
@@ -23,7 +27,6 @@ struct LaunchItem {
 // tile per launch alive. PARALIA_KCHAIN overrides the length (experiments: it changes
 // the rounding).
 int plan_kchain_len(bool bounded_cache, int ki0, int max_parts);
-
 // What the band sizes of a unit are derived from. The rho values are times relative to one
 // tile product (one launch of one k tile) on the unit: what it costs the unit's own host
 // link to bring in one more tile row of A (rho_a), one more tile column of B (rho_b) per k

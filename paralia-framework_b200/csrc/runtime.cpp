@@ -120,31 +120,55 @@ int resolve_operand_location(const void* ptr, int loc_in, size_t bytes, int ngpu
     return fail(PARALIA_ERR_INVALID_ARG, "operand declared on the host but the pointer is on GPU %d",
                 actual);
   *loc_out = loc;
-  if (loc == -1 && bytes > 0) {
-    // Page-locked only if both ends are: an operand that is a sub-view of a larger matrix can
-    // start inside a range someone registered and run past its end.
-    bool tail_pinned = pinned;
-    if (pinned && bytes > 1)
-      pointer_location(static_cast<const char*>(ptr) + bytes - 1, &tail_pinned);
-    if (!(pinned && tail_pinned)) {
-      const double t0 = wall_ms();
-      cudaError_t e = pinned ? cudaErrorHostMemoryAlreadyRegistered
-                             : cudaHostRegister(const_cast<void*>(ptr), bytes, cudaHostRegisterPortable);
-      if (e == cudaErrorHostMemoryAlreadyRegistered) {
-        // Overlaps a range that is registered already (interleaved views of one parent): the
-        // operand is used as pageable memory, which is correct, only slower.
-        cudaGetLastError();
-      } else if (e != cudaSuccess) {
-        cudaGetLastError();
-        return fail(PARALIA_ERR_CUDA, "cannot page-lock a host operand of %zu bytes: %s", bytes,
-                    cudaGetErrorString(e));
-      } else {
-        pin->ptr = ptr;
-        pin->registered = true;
-      }
-      if (pin_ms) *pin_ms += wall_ms() - t0;
+  if (loc == -1 && bytes > 0 && pin) {
+    HostRange r{ptr, bytes};
+    return pin_host_ranges(&r, 1, pin, pin_ms);
+  }
+  return PARALIA_OK;
+}
+
+// Page-lock the host ranges that are not page-locked yet. Ranges that overlap (operands that
+// are interleaved views of one parent matrix: their address ranges interleave column by
+// column) are registered as one range: CUDA neither registers a range that overlaps a
+// registered one nor copies asynchronously from a half-registered range. pins[i] receives
+// the registration made on behalf of range i (several ranges may share one; it is recorded
+// with the first of them).
+int pin_host_ranges(const HostRange* ranges, int n, HostPin* pins, double* pin_ms) {
+  struct Need { uintptr_t lo, hi; int first; };
+  std::vector<Need> need;
+  for (int i = 0; i < n; ++i) {
+    if (!ranges[i].ptr || ranges[i].bytes == 0) continue;
+    const char* base = static_cast<const char*>(ranges[i].ptr);
+    bool head = false, tail = false;
+    if (pointer_location(base, &head) >= 0) continue;   // not host memory: nothing to pin
+    pointer_location(base + ranges[i].bytes - 1, &tail);
+    if (head && tail) continue;                          // page-locked already
+    need.push_back({reinterpret_cast<uintptr_t>(base),
+                    reinterpret_cast<uintptr_t>(base) + ranges[i].bytes, i});
+  }
+  std::sort(need.begin(), need.end(), [](const Need& a, const Need& b) { return a.lo < b.lo; });
+  std::vector<Need> merged;
+  for (const Need& r : need) {
+    if (!merged.empty() && r.lo < merged.back().hi) {
+      merged.back().hi = std::max(merged.back().hi, r.hi);
+      merged.back().first = std::min(merged.back().first, r.first);
+    } else {
+      merged.push_back(r);
     }
   }
+  const double t0 = wall_ms();
+  for (const Need& r : merged) {
+    cudaError_t e = cudaHostRegister(reinterpret_cast<void*>(r.lo), r.hi - r.lo, cudaHostRegisterPortable);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      for (int i = 0; i < n; ++i) pins[i].release();
+      return fail(PARALIA_ERR_CUDA, "cannot page-lock a host operand of %zu bytes: %s",
+                  (size_t)(r.hi - r.lo), cudaGetErrorString(e));
+    }
+    pins[r.first].ptr = reinterpret_cast<const void*>(r.lo);
+    pins[r.first].registered = true;
+  }
+  if (pin_ms && !merged.empty()) *pin_ms += wall_ms() - t0;
   return PARALIA_OK;
 }
 

@@ -135,9 +135,18 @@ struct HostPin {
   void release();
 };
 
+// Page-lock host ranges that are not page-locked yet; overlapping ranges are registered as
+// one. pins[i] (n entries) receive the registrations, to be released by the caller.
+struct HostRange {
+  const void* ptr;
+  size_t bytes;
+};
+int pin_host_ranges(const HostRange* ranges, int n, HostPin* pins, double* pin_ms);
+
 // Check the location a caller declared for an operand (PARALIA_LOC_AUTO = ask the driver)
 // against where the pointer really lives, and page-lock `bytes` of it if it is pageable
-// host memory. *loc_out receives -1 (host) or the GPU id.
+// host memory and `pin` is not null (callers with several host operands pass null and pin
+// them together with pin_host_ranges). *loc_out receives -1 (host) or the GPU id.
 int resolve_operand_location(const void* ptr, int loc_in, size_t bytes, int ngpu, int* loc_out,
                              HostPin* pin, double* pin_ms);
 

@@ -138,7 +138,9 @@ def run_level3(pl, a, routine: str) -> dict:
                tflops_best=flops / min(times) / 1e12,
                tflops_device_best=flops / (min(dev_ms) * 1e-3) / 1e12,
                h2d_bytes=rep.h2d_bytes, d2h_bytes=rep.d2h_bytes, p2p_bytes=rep.p2p_bytes,
-               launches=rep.kernel_launches, pred_t=rep.pred_t, grid=[rep.grid_d1, rep.grid_d2])
+               launches=rep.kernel_launches, pred_t=rep.pred_t, grid=[rep.grid_d1, rep.grid_d2],
+               phases_ms={"fill": rep.fill_ms, "last_kernel_end": rep.exec_end_ms,
+                          "h2d_end": rep.h2d_end_ms, "device": rep.device_ms})
     for p, loc in zip(bufs, (a.locA, a.locB, a.locC)):
         pl.free(p, loc)
     return out

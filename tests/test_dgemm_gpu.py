@@ -123,7 +123,9 @@ def test_dgemm_cfg1_shape(pl, orc):
     rep = pl.dgemm("N", "N", M, N, K, 1.25, A, lda, B, ldb, 0.75, C, ldc,
                    ctl=pl.make_ctl(units=[0]))
     assert orc.normwise_rel_err(C, want) <= tol(K)
-    assert rep.T == 2048
+    # the tile is the model's choice: a streamed problem of this size wants tiles small enough
+    # to overlap the host link with the kernels, large enough for the kernel to be efficient
+    assert rep.T in (512, 768, 1024, 1280, 1536, 2048) and rep.pred_t > 0
 
 
 @pytest.mark.parametrize("ta,tb", [("N", "N"), ("T", "N"), ("N", "T")])
