@@ -244,6 +244,8 @@ def main(argv=None):
     ap.add_argument("db")
     ap.add_argument("--gpus", type=int, default=0, help="GPUs to calibrate links for (0 = all)")
     ap.add_argument("--quick", action="store_true")
+    ap.add_argument("--tables-only", action="store_true",
+                    help="measure only the kernel tables of GPU 0 (no links)")
     ap.add_argument("--links-only", action="store_true",
                     help="measure only the links and the host aggregate (the tile tables of "
                          "one GPU serve every identical GPU)")
@@ -257,8 +259,9 @@ def main(argv=None):
     if not a.links_only:
         build_exec(pl, db, 0, a.quick)      # identical GPUs: device 0's curve serves all
         build_level1(pl, db, 0, a.quick)
-    build_links(pl, db, [-1] + list(range(ngpu)), a.quick)
-    build_host_aggregate(pl, db, ngpu, a.quick)
+    if not a.tables_only:
+        build_links(pl, db, [-1] + list(range(ngpu)), a.quick)
+        build_host_aggregate(pl, db, ngpu, a.quick)
     peak = max(pl.bench_dmma_peak(0, s, 20000) for s in (884, 1688, 16816))
     (db / "Processed" / "fp64_tensor_peak_dev-0.log").write_text(f"{peak:e}\n")
     print(f"database written to {db} ({ngpu} GPU(s))")

@@ -342,7 +342,7 @@ def test_predictor_mode_needs_no_gpu_with_a_unit_list(pl, capsys):
     one = runner.main(["dgemm_predict", "1", "1", "-1", "-1", "N", "N", "1", "1",
                        "32768", "32768", "32768", "-1", "-1", "-1", "-1"])
     capsys.readouterr()
-    assert one["T"] in (4096, 8192) and 1.9 < one["pred_t"] < 2.2
+    assert 4096 <= one["T"] <= 8192 and one["T"] % 256 == 0 and 1.9 < one["pred_t"] < 2.2
 
 
 @pytest.mark.parametrize("dims,T,units", [((32768, 32768, 32768), 2048, 8), ((32768, 32768, 32768), 4096, 1),
