@@ -836,7 +836,28 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
     tuned = hit->second.tuned;
     reused = true;
   } else {
-    rc = autotune_gemm(mi_in, ngpu, &eff_ctl, &tuned);
+    if (grp && grp->world() > 1 && eff_ctl.T <= 0) {
+      // The tile edge of a group call is chosen for the whole problem on all ranks' GPUs (this
+      // rank's block times the device grid), not for one GPU working alone on its block: the
+      // ranks share the host link, so the fill, drain and link terms are those of the group.
+      // Every rank has a block of the same shape and so arrives at the same T.
+      int gd1, gd2;
+      grp->grid(&gd1, &gd2);
+      GemmModelInput whole = mi_in;
+      whole.M = M * gd1;
+      whole.N = N * gd2;
+      paralia_ctl all = eff_ctl;
+      all.active_unit_num = std::min(grp->world(), PARALIA_MAX_UNITS);
+      for (int i = 0; i < all.active_unit_num; ++i) all.active_unit_id_list[i] = i;
+      paralia_report whole_rep;
+      rc = autotune_gemm(whole, all.active_unit_num, &all, &whole_rep);
+      if (rc != PARALIA_OK) { cleanup_pins(); return rc; }
+      eff_ctl.T = whole_rep.T;
+      rc = autotune_gemm(mi_in, ngpu, &eff_ctl, &tuned);
+      tuned.pred_t = whole_rep.pred_t;
+    } else {
+      rc = autotune_gemm(mi_in, ngpu, &eff_ctl, &tuned);
+    }
     if (rc != PARALIA_OK) { cleanup_pins(); return rc; }
     if (plan_cache.size() >= 100) plan_cache.clear();   // reference: PROBLEM_MD_CACHE = 100
     plan_cache[key] = CachedPlan{tuned};
