@@ -526,6 +526,8 @@ def run_inproc(pl, torch, args, ngpu, n, check):
             "tile": int(rep.T), "device_grid": [rep.grid_d1, rep.grid_d2],
             "h2d_bytes_per_step": h2d // steps, "d2h_bytes_per_step": d2h // steps,
             "gpu_launches": launches, "p2p_bytes_per_step": int(rep.p2p_bytes),
+            "last_call_ms": {"host": rep.host_ms, "device": rep.device_ms, "plan": rep.plan_ms,
+                             "pin": rep.pin_ms, "alloc": rep.alloc_ms},
             "phases_ms": {"fill": rep.fill_ms, "last_kernel_end": rep.exec_end_ms,
                           "h2d_end": rep.h2d_end_ms, "device": rep.device_ms},
             "timing": "wall clock around the blocking calls (one process drives all GPUs)",

@@ -952,7 +952,9 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
     // of free memory plus the slab already held). A clamped slab recycles its blocks.
     int64_t cap = need;
     if (eff_ctl.cache_limit > 0) cap = std::min<int64_t>(cap, eff_ctl.cache_limit / (int64_t)g.block_bytes());
-    {
+    // (a slab that already holds the working set needs no look at the free memory; the query
+    // costs about a millisecond per GPU)
+    if ((size_t)need * g.block_bytes() > rt.dev(u.dev).slab_bytes) {
       size_t free_b = 0, total_b = 0;
       if (cudaSetDevice(u.dev) == cudaSuccess && cudaMemGetInfo(&free_b, &total_b) == cudaSuccess) {
         const double avail = 0.9 * ((double)free_b + (double)rt.dev(u.dev).slab_bytes);
