@@ -6,10 +6,12 @@
 // the parameter block built at Library_scheduler/src/Functions/dgemm.cpp:181-197.
 //
 // Blackwell's tcgen05 tensor path has no FP64 kind, so the FP64 tensor cores are driven
-// with warp-level mma.sync (DMMA). One CTA (288 threads) computes one work item:
-//   * warp 8 is the producer: one lane issues TMA 3-D tiled loads (128-byte swizzle, no
-//     multicast) for a 128 x 16 slice of A and a 16 x 128 slice of B per stage into a
-//     6-stage ring, completion signalled on "full" mbarriers;
+// with warp-level mma.sync (DMMA). One CTA computes one work item:
+//   * a producer issues TMA 3-D tiled loads (128-byte swizzle, no multicast) for a 128 x 16
+//     slice of A and a 16 x 128 slice of B per stage into a 6-stage ring, completion signalled
+//     on "full" mbarriers. The producer is one lane of an extra warp, of an extra warpgroup
+//     that gives its registers to the consumers, or of consumer warp 0 itself (the three
+//     modes of dgemm_tile.cuh; the fastest differs by storage order);
 //   * warps 0-7 are consumers: each owns a piece of the item's C tile, reads operand
 //     fragments from the swizzled stage with conflict-free 64-bit loads and issues m16n8k8
 //     DMMA; a warp releases the stage on an "empty" mbarrier;
@@ -114,13 +116,58 @@ struct Shape {
   static constexpr int IB = QUARTER ? 1 : 2;
 };
 
+// Where the producer stands in the launch's list of k parts.
+struct ProdCursor {
+  int it = 0;     // next k step to issue
+  int part = 0;   // its part
+  int kk = 0;     // its offset inside the part
+};
+
+// Issue the TMA loads of k step c.it into its ring slot and advance the cursor. One thread.
+template <bool A_KC, bool B_KC>
+__device__ __forceinline__ void issue_stage(const CUtensorMap* mapA, const CUtensorMap* mapB,
+                                            const DgemmArgs& args, const Item& w,
+                                            unsigned char* smem, uint64_t* full_bar,
+                                            ProdCursor& c) {
+  const DgemmKPart& part = args.parts[c.part];
+  const int s = c.it % DG_STAGES;
+  const int kk = c.kk;
+  unsigned char* sA = smem + s * DG_STAGE_BYTES;
+  unsigned char* sB = sA + DG_BM * DG_BK * 8;
+  mbar_expect_tx(&full_bar[s], DG_STAGE_BYTES);
+  if (A_KC) {
+    tma_load_3d(sA, mapA, &full_bar[s], part.a_k + kk, part.a_m + w.tm0, part.a_z);
+  } else {
+#pragma unroll
+    for (int c2 = 0; c2 < DG_BM / 16; ++c2)
+      tma_load_3d(sA + c2 * 2048, mapA, &full_bar[s], part.a_m + w.tm0 + c2 * 16, part.a_k + kk,
+                  part.a_z);
+  }
+  if (B_KC) {
+    tma_load_3d(sB, mapB, &full_bar[s], part.b_k + kk, part.b_n + w.tn0, part.b_z);
+  } else {
+#pragma unroll
+    for (int c2 = 0; c2 < DG_BN / 16; ++c2)
+      tma_load_3d(sB + c2 * 2048, mapB, &full_bar[s], part.b_n + w.tn0 + c2 * 16, part.b_k + kk,
+                  part.b_z);
+  }
+  ++c.it;
+  c.kk += DG_BK;
+  if (c.kk >= part.klen) {
+    c.kk = 0;
+    ++c.part;
+  }
+}
+
 // Main loop and epilogue of one item for one consumer warp. Returns false if a wait gave up.
-template <bool A_KC, bool B_KC, bool QUARTER>
+template <bool A_KC, bool B_KC, bool QUARTER, int MODE>
 __device__ __forceinline__ bool consume_item(const DgemmArgs& args, const Item& w,
-                                             const unsigned char* smem, uint64_t* full_bar,
+                                             unsigned char* smem, uint64_t* full_bar,
                                              uint64_t* empty_bar, volatile int* abort_flag,
-                                             int warp, int lane) {
+                                             int warp, int lane, const CUtensorMap* mapA,
+                                             const CUtensorMap* mapB) {
   using S = Shape<QUARTER>;
+  constexpr bool FOLD = MODE == DG_MODE_FOLD;
   const int g = lane >> 2;
   const int t = lane & 3;
   const int wn = warp & 3;   // column slice of the item
@@ -151,13 +198,50 @@ __device__ __forceinline__ bool consume_item(const DgemmArgs& args, const Item& 
   int total = 0;
   for (int p = 0; p < args.nparts; ++p) total += (args.parts[p].klen + DG_BK - 1) / DG_BK;
 
+  // Fold: warp 0's first lane is the producer as well: it starts the ring with the first
+  // DG_STAGES - DG_FOLD_LAG k steps and, at the top of iteration `it`, refills the slot that
+  // was used DG_FOLD_LAG iterations ago (every warp has normally released it by then).
+  ProdCursor cur;
+  const bool producer = FOLD && (warp == 0 && lane == 0);
+  if (producer && total > 0) {
+    prefetch_tensormap(mapA);
+    prefetch_tensormap(mapB);
+    const int first = total < DG_STAGES - DG_FOLD_LAG ? total : DG_STAGES - DG_FOLD_LAG;
+    for (int j = 0; j < first; ++j)
+      issue_stage<A_KC, B_KC>(mapA, mapB, args, w, smem, full_bar, cur);
+  }
+
   for (int it = 0; it < total; ++it) {
     const int s = it % DG_STAGES;
     const uint32_t par = (uint32_t)((it / DG_STAGES) & 1);
+    if (FOLD && warp == 0) {
+      if (producer && cur.it < total) {
+        bool ok = true;
+        if (it >= DG_FOLD_LAG) {
+          const int u = it - DG_FOLD_LAG;
+          ok = mbar_wait_bounded(&empty_bar[u % DG_STAGES], (uint32_t)((u / DG_STAGES) & 1),
+                                 abort_flag);
+          if (!ok && !*abort_flag) {
+            *abort_flag = 1;
+            atomicExch(args.status, KERR_EMPTY_WAIT_TIMEOUT);
+          }
+        }
+        if (ok) issue_stage<A_KC, B_KC>(mapA, mapB, args, w, smem, full_bar, cur);
+      }
+      __syncwarp();
+    }
     if (!mbar_wait_bounded(&full_bar[s], par, abort_flag)) {
       if (!*abort_flag) {
         *abort_flag = 1;
         atomicExch(args.status, KERR_FULL_WAIT_TIMEOUT);
+      }
+      if (producer) {
+        // let the copies already issued land before the CTA's shared memory is released
+        for (int j = it; j < cur.it; ++j) {
+          int zero = 0;
+          if (!mbar_wait_bounded(&full_bar[j % DG_STAGES], (uint32_t)((j / DG_STAGES) & 1), &zero))
+            atomicExch(args.status, KERR_DRAIN_TIMEOUT);
+        }
       }
       return false;
     }
@@ -230,8 +314,8 @@ __device__ __forceinline__ bool consume_item(const DgemmArgs& args, const Item& 
   return true;
 }
 
-template <bool A_KC, bool B_KC, bool QUARTER>
-__global__ void __launch_bounds__(DG_THREADS, 1)
+template <bool A_KC, bool B_KC, bool QUARTER, int MODE>
+__global__ void __launch_bounds__(dg_threads(MODE), 1)
 dgemm_tile_kernel(const __grid_constant__ CUtensorMap mapA,
                   const __grid_constant__ CUtensorMap mapB,
                   const __grid_constant__ DgemmArgs args) {
@@ -258,9 +342,10 @@ dgemm_tile_kernel(const __grid_constant__ CUtensorMap mapA,
   }
   __syncthreads();
 
-  if (warp == DG_CONSUMER_WARPS) {
+  if (MODE != DG_MODE_FOLD && warp >= DG_CONSUMER_WARPS) {
     // ------------------------------ producer ------------------------------
-    if (lane == 0) {
+    if (MODE == DG_MODE_GROUP) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    if (warp == DG_CONSUMER_WARPS && lane == 0) {
       if (args.nparts > 0) {
         prefetch_tensormap(&mapA);
         prefetch_tensormap(&mapB);
@@ -319,7 +404,9 @@ dgemm_tile_kernel(const __grid_constant__ CUtensorMap mapA,
   }
 
   // -------------------------------- consumers --------------------------------
-  consume_item<A_KC, B_KC, QUARTER>(args, w, smem, full_bar, empty_bar, abort_flag, warp, lane);
+  if (MODE == DG_MODE_GROUP) asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+  consume_item<A_KC, B_KC, QUARTER, MODE>(args, w, smem, full_bar, empty_bar, abort_flag, warp, lane,
+                                    &mapA, &mapB);
 }
 
 // ------------------------------------------------------------------------------
@@ -475,25 +562,38 @@ cudaError_t launch_bounded_wait_selftest(int* status, long long budget_clocks, c
 }
 
 namespace {
+// CTA shape of the whole items of a storage-order pair, chosen by measurement on B200
+// (TFLOP/s of a 4096-wide tile, eight launches in flight: warp / fold / group):
+//   A row-contiguous, B k-contiguous (NN)  34.45 / 35.32 / 34.76
+//   A k-contiguous,   B k-contiguous (TN)  35.59 / 34.97 / 35.49
+//   A row-contiguous, B row-contiguous (NT) 34.38 / 29.86 / 34.98
+//   A k-contiguous,   B row-contiguous (TT) 34.78 / 35.31 / 34.81
+// Quarter items always run with the producer warp.
+template <bool A_KC, bool B_KC>
+constexpr int dgemm_mode_for() {
+  return (A_KC != B_KC) ? DG_MODE_FOLD : (A_KC ? DG_MODE_WARP : DG_MODE_GROUP);
+}
+
 template <bool A_KC, bool B_KC>
 cudaError_t configure_pair() {
-  cudaError_t e = cudaFuncSetAttribute(dgemm_tile_kernel<A_KC, B_KC, false>,
+  cudaError_t e = cudaFuncSetAttribute(dgemm_tile_kernel<A_KC, B_KC, false, dgemm_mode_for<A_KC, B_KC>()>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, DG_SMEM_BYTES);
   if (e != cudaSuccess) return e;
-  return cudaFuncSetAttribute(dgemm_tile_kernel<A_KC, B_KC, true>,
+  return cudaFuncSetAttribute(dgemm_tile_kernel<A_KC, B_KC, true, DG_MODE_WARP>,
                               cudaFuncAttributeMaxDynamicSharedMemorySize, DG_SMEM_BYTES);
 }
 
 template <bool A_KC, bool B_KC>
 cudaError_t launch_pair(const CUtensorMap& mapA, const CUtensorMap& mapB, const DgemmArgs& args,
                         cudaStream_t stream) {
-  const dim3 block(DG_THREADS);
+  constexpr int MODE = dgemm_mode_for<A_KC, B_KC>();
   if (args.full_items > 0)
-    dgemm_tile_kernel<A_KC, B_KC, false><<<dim3(args.full_items), block, DG_SMEM_BYTES, stream>>>(
-        mapA, mapB, args);
+    dgemm_tile_kernel<A_KC, B_KC, false, MODE>
+        <<<dim3(args.full_items), dim3(dg_threads(MODE)), DG_SMEM_BYTES, stream>>>(mapA, mapB, args);
   if (args.quarter_items > 0)
-    dgemm_tile_kernel<A_KC, B_KC, true><<<dim3(args.quarter_items), block, DG_SMEM_BYTES, stream>>>(
-        mapA, mapB, args);
+    dgemm_tile_kernel<A_KC, B_KC, true, DG_MODE_WARP>
+        <<<dim3(args.quarter_items), dim3(dg_threads(DG_MODE_WARP)), DG_SMEM_BYTES, stream>>>(
+            mapA, mapB, args);
   return cudaGetLastError();
 }
 }  // namespace

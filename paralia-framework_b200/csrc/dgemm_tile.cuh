@@ -12,7 +12,21 @@ constexpr int DG_BN = 128;      // columns of C per CTA
 constexpr int DG_BK = 16;       // k per pipeline stage (16 doubles = one 128-byte swizzle row)
 constexpr int DG_STAGES = 6;    // 6 x 32 KB of operand tiles in flight
 constexpr int DG_CONSUMER_WARPS = 8;
-constexpr int DG_THREADS = (DG_CONSUMER_WARPS + 1) * 32;  // + one TMA producer warp
+// Three CTA shapes of the same kernel (same stages, same arithmetic, same result bits):
+//   DG_MODE_WARP   one extra warp is the TMA producer (288 threads; three warps share one
+//                  scheduler's registers, so a thread gets at most 168);
+//   DG_MODE_FOLD   no producer warp: lane 0 of consumer warp 0 issues the loads between its
+//                  own MMAs (256 threads, up to 255 registers per thread);
+//   DG_MODE_GROUP  a whole producer warpgroup that hands most of its registers to the
+//                  consumers with setmaxnreg (384 threads, consumers run with 232).
+// Which one is fastest depends on the storage order of the operands (how many TMA boxes a
+// stage takes and how the fragment loads are addressed); launch_dgemm_tile picks by
+// measurement, see dgemm_mode_for().
+enum : int { DG_MODE_WARP = 0, DG_MODE_FOLD = 1, DG_MODE_GROUP = 2 };
+constexpr int dg_threads(int mode) {
+  return (DG_CONSUMER_WARPS + (mode == DG_MODE_FOLD ? 0 : (mode == DG_MODE_GROUP ? 4 : 1))) * 32;
+}
+constexpr int DG_FOLD_LAG = 2;  // fold: a stage is refilled this many iterations after its use
 constexpr int DG_STAGE_BYTES = (DG_BM + DG_BN) * DG_BK * 8;
 constexpr int DG_SMEM_BYTES = DG_STAGES * DG_STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 constexpr int DG_MAX_PARTS = 64;

@@ -264,6 +264,10 @@ def main(argv=None):
         build_host_aggregate(pl, db, ngpu, a.quick)
     peak = max(pl.bench_dmma_peak(0, s, 20000) for s in (884, 1688, 16816))
     (db / "Processed" / "fp64_tensor_peak_dev-0.log").write_text(f"{peak:e}\n")
+    # TF32 tcgen05 issue rate of the SGEMM kernel's MMA shape; the 3xTF32 kernel's roofline
+    # is a third of it
+    tf32 = max(pl.bench_tf32_peak(0, 20000) for _ in range(3))
+    (db / "Processed" / "tf32_tensor_peak_dev-0.log").write_text(f"{tf32:e}\n")
     print(f"database written to {db} ({ngpu} GPU(s))")
 
 
