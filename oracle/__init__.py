@@ -21,6 +21,7 @@ package. The shipped library never does.
 from __future__ import annotations
 
 import ctypes as C
+import os
 import subprocess
 from pathlib import Path
 
@@ -38,8 +39,10 @@ def build() -> Path:
     checkout is present)."""
     subprocess.run(["make", "-C", str(ORACLE_DIR), "liboracle.so"], check=True,
                    capture_output=True)
-    if Path("/root/reference/Autotuner/src/Subkernel_distributions.cpp").exists():
-        subprocess.run(["make", "-C", str(ORACLE_DIR), "_ref"], check=True, capture_output=True)
+    ref = os.environ.get("PARALIA_REFERENCE_DIR", "")
+    if ref and (Path(ref) / "Autotuner/src/Subkernel_distributions.cpp").exists():
+        subprocess.run(["make", "-C", str(ORACLE_DIR), "_ref", f"REF={ref}"], check=True,
+                       capture_output=True)
     return LIB_PATH
 
 
