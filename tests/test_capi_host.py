@@ -294,6 +294,29 @@ def test_packaged_database_loads_and_fills_unmeasured_links(pl):
     assert 0.22 < t8 < 0.33
 
 
+def test_packaged_database_is_complete_for_an_eight_gpu_box(pl):
+    """The shipped calibration database holds what the autotuner reads: tile tables of the four
+    routines, both tensor peaks, the host aggregate table and a link file for every ordered
+    pair of the nine locations (host and eight GPUs), each with its two model lines."""
+    proc = pl.DEFAULT_DB / "Processed"
+    for routine in ("Dgemm", "Sgemm", "Daxpy", "Ddot"):
+        rows = (proc / f"{routine}_lookup-table_dev-0.log").read_text().strip().splitlines()
+        assert len(rows) >= 20, routine
+    fp64 = float((proc / "fp64_tensor_peak_dev-0.log").read_text())
+    tf32 = float((proc / "tf32_tensor_peak_dev-0.log").read_text())
+    assert 30.0 < fp64 < 45.0            # TFLOP/s, DMMA register loop
+    assert 900.0 < tf32 < 1300.0         # TFLOP/s, tcgen05 kind::tf32 issue rate
+    agg = (proc / "Host-Link-Aggregate.log").read_text().split()
+    assert {"H2D", "D2H", "BIDIR"} <= set(agg)
+    locs = [-1] + list(range(8))
+    for dst in locs:
+        for src in locs:
+            if dst == src:
+                continue
+            text = (proc / f"Link-Stats_loc_dest-{dst}_loc_src-{src}.log").read_text()
+            assert "Intercept" in text and "Coefficient" in text, (dst, src)
+
+
 def test_sweep_matrix_is_the_reference_evaluation_matrix(pl):
     # Benchmarking/Full_performance_evaluation.in: 10 placement scenarios; squares
     # 2048..22528 step 1024; thin K = MN/{2,8,32} for MN 8192..32768 step 4096; fat K
