@@ -385,6 +385,9 @@ int PARALiA_bench_tile_sgemm(int dev, int64_t T, int reps, double* mean_s);
  * mean seconds per tile. */
 int PARALiA_bench_tile_daxpy(int dev, int64_t N, int reps, double* mean_s);
 int PARALiA_bench_tile_ddot(int dev, int64_t N, int reps, double* mean_s);
+/* One square T x T DGEMV tile (TransA 'N' or 'T') on device-resident operands (reference:
+ * Database_builder/CuCuBLAS/src/dgemv_microbench.cu:127-190); mean seconds per tile. */
+int PARALiA_bench_tile_dgemv(int dev, char TransA, int64_t T, int reps, double* mean_s);
 /* All host links of GPUs 0..ngpu-1 at once, `reps` pinned copies of `bytes` each per GPU
  * and direction. mode 0: host -> GPU only, 1: GPU -> host only, 2: both directions together.
  * *gbs receives the aggregate GB/s per direction. No counterpart in the reference. */

@@ -176,6 +176,7 @@ SIGNATURES = {
                                                     C.c_int, C.c_int, C.POINTER(_dbl)]),
     "PARALiA_bench_tile_daxpy": (C.c_int, [C.c_int, _i64, C.c_int, C.POINTER(_dbl)]),
     "PARALiA_bench_tile_ddot": (C.c_int, [C.c_int, _i64, C.c_int, C.POINTER(_dbl)]),
+    "PARALiA_bench_tile_dgemv": (C.c_int, [C.c_int, _chr, _i64, C.c_int, C.POINTER(_dbl)]),
     "PARALiA_bench_host_aggregate": (C.c_int, [C.c_int, C.c_int, _i64, C.c_int, C.POINTER(_dbl)]),
     "PARALiA_autotune_vec": (C.c_int, [C.c_int, _i64, C.c_int, C.c_int, _ctl_p, _rep_p]),
     "PARALiA_model_host_link": (C.c_int, [C.c_int, C.c_int, _i64, C.c_int, C.c_int, C.POINTER(_i32),
@@ -514,6 +515,13 @@ def bench_dmma_peak(dev=0, shape=1688, iters=20000) -> float:
 def bench_tile_dgemm_chain(dev, TransA, TransB, T, chain, reps) -> float:
     v = _dbl()
     _check(lib().PARALiA_bench_tile_dgemm_chain(dev, _c(TransA), _c(TransB), T, chain, reps, C.byref(v)))
+    return v.value
+
+
+def bench_tile_dgemv(dev, trans, T, reps=8) -> float:
+    """Mean seconds of one square T x T DGEMV tile on device-resident operands."""
+    v = _dbl()
+    _check(lib().PARALiA_bench_tile_dgemv(dev, _c(trans), int(T), int(reps), C.byref(v)))
     return v.value
 
 

@@ -3,6 +3,7 @@
 //
 // Reference: Database_builder/CuCuBLAS/src/daxpy_microbench.cu:26-231 and
 // ddot_microbench.cu:26-228 (time one device-resident vector tile per length),
+// dgemv_microbench.cu:127-190 (one square matrix-vector tile per edge),
 // transfer_link_microbench.cu:186-218 (a link while another link is busy). The aggregate
 // measurement has no counterpart there: it times all host links of n GPUs at once, which is
 // what shows the cap of this class of host (root complex / host memory) that pairwise
@@ -13,6 +14,7 @@
 
 #include "autotune.hpp"
 #include "level1.cuh"
+#include "level2.cuh"
 #include "runtime.hpp"
 #include "sgemm_tile.cuh"
 
@@ -71,12 +73,72 @@ int bench_level1(bool is_dot, int dev, int64_t N, int reps, double* mean_s) {
   return rc;
 }
 
+// One square T x T matrix-vector tile on device-resident operands, as the reference's
+// Database_builder/CuCuBLAS/src/dgemv_microbench.cu:127-190 times cublasDgemv.
+int bench_level2(bool trans, int dev, int64_t T, int reps, double* mean_s) {
+  if (!mean_s || reps <= 0 || T <= 0 || T > (1 << 17))
+    return fail(PARALIA_ERR_INVALID_ARG, "bad bench arguments");
+  Runtime& rt = Runtime::get();
+  PL_TRY(rt.init());
+  DeviceGuard guard;
+  PL_TRY(rt.ensure_device(dev));
+  PL_CUDA(cudaSetDevice(dev));
+  DeviceCtx& dc = rt.dev(dev);
+  cudaStream_t s = dc.exec[0];
+  // rotate through enough copies of the matrix that a tile is never served from L2
+  const size_t bytes = (size_t)T * T * 8;
+  const int slots = (int)std::max<size_t>(2, std::min<size_t>(16, ((size_t)192 << 20) / bytes + 1));
+  const int slices = trans ? 0 : gemv_n_slices((int)T, (int)T);
+  double *a = nullptr, *x = nullptr, *y = nullptr, *partial = nullptr;
+  cudaError_t e = cudaMalloc(&a, bytes * slots);
+  if (e == cudaSuccess) e = cudaMalloc(&x, (size_t)T * 8);
+  if (e == cudaSuccess) e = cudaMalloc(&y, (size_t)T * 8);
+  if (e == cudaSuccess && slices > 0) e = cudaMalloc(&partial, (size_t)slices * T * 8);
+  int rc = PARALIA_OK;
+  if (e != cudaSuccess) rc = fail(PARALIA_ERR_OUT_OF_MEMORY, "bench buffers: %s", cudaGetErrorString(e));
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  if (rc == PARALIA_OK) {
+    launch_fill_f64(a, (int64_t)T * T * slots, 42, 0, s);
+    launch_fill_f64(x, T, 43, 0, s);
+    launch_fill_f64(y, T, 44, 0, s);
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    int launches = 0;
+    auto one = [&](int i) {
+      return launch_dgemv_tile(trans, (int)T, (int)T, 1.0, a + (size_t)(i % slots) * T * T, T, x, 1,
+                               0.5, y, 1, partial, s, &launches);
+    };
+    for (int i = 0; i < 2 && e == cudaSuccess; ++i) e = one(i);
+    cudaEventRecord(e0, s);
+    for (int i = 0; i < reps && e == cudaSuccess; ++i) e = one(i + 2);
+    cudaEventRecord(e1, s);
+    if (e == cudaSuccess) e = cudaEventSynchronize(e1);
+    float ms = 0.f;
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, e0, e1);
+    if (e != cudaSuccess) rc = fail(PARALIA_ERR_CUDA, "level-2 benchmark failed: %s", cudaGetErrorString(e));
+    else *mean_s = ms * 1e-3 / reps;
+  }
+  if (e0) cudaEventDestroy(e0);
+  if (e1) cudaEventDestroy(e1);
+  cudaFree(a);
+  cudaFree(x);
+  cudaFree(y);
+  cudaFree(partial);
+  cudaGetLastError();
+  return rc;
+}
+
 }  // namespace
 }  // namespace paralia
 
 using namespace paralia;
 
 extern "C" {
+
+int PARALiA_bench_tile_dgemv(int dev, char TransA, int64_t T, int reps, double* mean_s) {
+  if (TransA != 'N' && TransA != 'T') return fail(PARALIA_ERR_INVALID_ARG, "TransA must be N or T");
+  return bench_level2(TransA == 'T', dev, T, reps, mean_s);
+}
 
 int PARALiA_bench_tile_daxpy(int dev, int64_t N, int reps, double* mean_s) {
   return bench_level1(false, dev, N, reps, mean_s);

@@ -180,6 +180,22 @@ def build_level1(pl, db: Path, dev: int, quick: bool):
         (db / "Processed" / f"{func}_lookup-table_dev-{dev}.log").write_text("\n".join(rows) + "\n")
 
 
+def build_level2(pl, db: Path, dev: int, quick: bool):
+    """Dgemv tile tables, one file per transpose as the reference writes them
+    (dgemv_microbench.cu:19-24,56-58,127-190): rows ``M,N, mean_t,W,J,margin,samples,bench_t``."""
+    raw = db / "Benchmark-Results"
+    rows = []
+    for trans in ("N", "T"):
+        raw_lines = []
+        for T in ((4096, 16384) if quick else range(2048, 32768 + 1, 2048)):
+            mean, err, cnt, bt = sample_until_confident(lambda: pl.bench_tile_dgemv(dev, trans, T, 8),
+                                                        budget_s=0.5)
+            raw_lines.append(f"{T},{T}, {mean:e},0,0,{err:e},{cnt},{bt:e}")
+            rows.append(f"{trans},{T},{T},{mean:e},0.000000e+00,0.000000e+00,{err:e},{cnt},{bt:e}")
+        (raw / f"cublasDgemv_dev-{dev}_TransA-{trans}_{VERSION}.log").write_text("\n".join(raw_lines) + "\n")
+    (db / "Processed" / f"Dgemv_lookup-table_dev-{dev}.log").write_text("\n".join(rows) + "\n")
+
+
 def build_host_aggregate(pl, db: Path, ngpu: int, quick: bool):
     """Aggregate host-link bandwidth against the number of GPUs copying at once."""
     counts = sorted({c for c in (1, 2, 4, 8, ngpu) if c <= ngpu})
@@ -259,6 +275,7 @@ def main(argv=None):
     if not a.links_only:
         build_exec(pl, db, 0, a.quick)      # identical GPUs: device 0's curve serves all
         build_level1(pl, db, 0, a.quick)
+        build_level2(pl, db, 0, a.quick)
     if not a.tables_only:
         build_links(pl, db, [-1] + list(range(ngpu)), a.quick)
         build_host_aggregate(pl, db, ngpu, a.quick)

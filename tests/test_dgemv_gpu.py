@@ -155,3 +155,16 @@ def test_dgemv_empty_inner_dimension_scales_y(pl, ta, beta):
     x = np.zeros(1)
     pl.dgemv(ta, M, N, 1.25, A, max(M, 1), x, 1, beta, y, 1, ctl=pl.make_ctl(units=[0]))
     assert np.array_equal(y, want)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("ta", ["N", "T"])
+def test_tile_dgemv_microbenchmark_is_hbm_bound(pl, ta):
+    """The calibration microbenchmark of the DGEMV tile (the reference's dgemv_microbench) moves
+    8 bytes per element of A: on a B200 a 16384-wide tile must stream well above 3 TB/s."""
+    T = 16384
+    t = pl.bench_tile_dgemv(0, ta, T, 4)
+    gbs = 8.0 * T * T / t / 1e9
+    assert 3000.0 < gbs < 9000.0, gbs
+    with pytest.raises(pl.ParaliaError):
+        pl.bench_tile_dgemv(0, "C", T, 4)
