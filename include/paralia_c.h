@@ -370,6 +370,9 @@ int PARALiA_bench_dmma_peak(int dev, int shape, int iters, double* tflops);
  * run; the 3xTF32 kernel's roofline is a third of it. A few thousand stages give the burst
  * figure, a few hundred thousand (about a second) the figure under the power cap. */
 int PARALiA_bench_tf32_peak(int dev, int stages, double* tflops);
+/* The same loop on operands drawn from uniform(-1, 1) instead of ones: the rate a real
+ * product can be issued at once the datapath toggles and the board's power limit applies. */
+int PARALiA_bench_tf32_peak_random(int dev, int stages, double* tflops);
 /* Time `reps` launches of the tile DGEMM on square T; returns mean seconds. */
 int PARALiA_bench_tile_dgemm(int dev, char TransA, char TransB, int64_t T, int reps,
                              double* mean_s);

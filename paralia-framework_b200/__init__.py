@@ -171,6 +171,7 @@ SIGNATURES = {
                                                  C.POINTER(_dbl)]),
     "PARALiA_bench_tile_sgemm": (C.c_int, [C.c_int, _i64, C.c_int, C.POINTER(_dbl)]),
     "PARALiA_bench_tf32_peak": (C.c_int, [C.c_int, C.c_int, C.POINTER(_dbl)]),
+    "PARALiA_bench_tf32_peak_random": (C.c_int, [C.c_int, C.c_int, C.POINTER(_dbl)]),
     "PARALiA_selftest_join_deadline": (C.c_int, [C.c_int, _dbl, _dbl]),
     "PARALiA_selftest_group_rendezvous": (C.c_int, [C.c_char_p, C.c_int, C.c_int, C.c_int, C.c_int,
                                                     C.c_int, C.c_int, C.POINTER(_dbl)]),
@@ -525,10 +526,12 @@ def bench_tile_dgemv(dev, trans, T, reps=8) -> float:
     return v.value
 
 
-def bench_tf32_peak(dev, stages) -> float:
-    """Dense TF32 TFLOP/s of the tcgen05 instruction shape the FP32 kernel issues."""
+def bench_tf32_peak(dev, stages, random_operands=False) -> float:
+    """Dense TF32 TFLOP/s of the tcgen05 instruction shape the FP32 kernel issues, on operands
+    of ones (the issue rate) or drawn from uniform(-1, 1) (what the power limit allows)."""
     v = _dbl()
-    _check(lib().PARALiA_bench_tf32_peak(dev, int(stages), C.byref(v)))
+    fn = lib().PARALiA_bench_tf32_peak_random if random_operands else lib().PARALiA_bench_tf32_peak
+    _check(fn(dev, int(stages), C.byref(v)))
     return v.value
 
 

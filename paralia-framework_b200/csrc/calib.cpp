@@ -148,7 +148,7 @@ int PARALiA_bench_tile_ddot(int dev, int64_t N, int reps, double* mean_s) {
   return bench_level1(true, dev, N, reps, mean_s);
 }
 
-int PARALiA_bench_tf32_peak(int dev, int stages, double* tflops) {
+static int bench_tf32_peak(int dev, int stages, bool random_operands, double* tflops) {
   if (!tflops || stages <= 0) return fail(PARALIA_ERR_INVALID_ARG, "bad bench arguments");
   Runtime& rt = Runtime::get();
   PL_TRY(rt.init());
@@ -162,9 +162,9 @@ int PARALiA_bench_tf32_peak(int dev, int stages, double* tflops) {
   PL_CUDA(cudaEventCreate(&e0));
   PL_CUDA(cudaEventCreate(&e1));
   cudaStream_t s = dc.exec[0];
-  cudaError_t e = launch_tf32_peak(std::min(stages, 2000), sms, dc.status_dev, s);   // warm-up
+  cudaError_t e = launch_tf32_peak(std::min(stages, 2000), sms, random_operands, dc.status_dev, s);   // warm-up
   if (e == cudaSuccess) e = cudaEventRecord(e0, s);
-  if (e == cudaSuccess) e = launch_tf32_peak(stages, sms, dc.status_dev, s);
+  if (e == cudaSuccess) e = launch_tf32_peak(stages, sms, random_operands, dc.status_dev, s);
   if (e == cudaSuccess) e = cudaEventRecord(e1, s);
   if (e == cudaSuccess) e = cudaEventSynchronize(e1);
   float ms = 0.f;
@@ -175,6 +175,14 @@ int PARALiA_bench_tf32_peak(int dev, int stages, double* tflops) {
   PL_TRY(rt.check_status(dev));
   *tflops = SG_PEAK_FLOP_PER_STAGE * (double)stages * sms / (ms * 1e-3) / 1e12;
   return PARALIA_OK;
+}
+
+int PARALiA_bench_tf32_peak(int dev, int stages, double* tflops) {
+  return bench_tf32_peak(dev, stages, false, tflops);
+}
+
+int PARALiA_bench_tf32_peak_random(int dev, int stages, double* tflops) {
+  return bench_tf32_peak(dev, stages, true, tflops);
 }
 
 int PARALiA_bench_host_aggregate(int ngpu, int mode, int64_t bytes, int reps, double* gbs) {

@@ -29,6 +29,8 @@
 // frees its tensor memory and exits.
 #include "sgemm_tile.cuh"
 
+#include <algorithm>
+
 #include "sm100_prims.cuh"
 
 namespace paralia {
@@ -402,7 +404,7 @@ sgemm_tile_kernel(const __grid_constant__ SgemmArgs args) {
 // kernel does. What it measures is the rate the tensor pipe sustains for this instruction
 // shape (M = 128, N = 256, K = 8, operands read from shared memory through no-swizzle
 // K-major descriptors): the roofline of the 3xTF32 kernel is a third of it.
-__global__ void __launch_bounds__(64, 1) tf32_peak_kernel(int stages, int* status) {
+__global__ void __launch_bounds__(64, 1) tf32_peak_kernel(int stages, int random_operands, int* status) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
@@ -411,7 +413,18 @@ __global__ void __launch_bounds__(64, 1) tf32_peak_kernel(int stages, int* statu
   __shared__ int abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int i = threadIdx.x; i < SG_STAGE_BYTES / 4; i += blockDim.x)
-    reinterpret_cast<float*>(smem)[i] = 1.0f;
+  {
+    // constant operands measure the issue rate of the tensor pipe; operands drawn from
+    // uniform(-1, 1) (TF32-exact) toggle the datapath like a real product does, which is what
+    // the board's power limit sees
+    float v = 1.0f;
+    if (random_operands) {
+      uint32_t h = (uint32_t)i * 2654435761u ^ (blockIdx.x * 40503u + 0x9E3779B9u);
+      h ^= h >> 16; h *= 0x7feb352du; h ^= h >> 15; h *= 0x846ca68bu; h ^= h >> 16;
+      v = tf32_round((float)(h >> 8) * (2.0f / 16777216.0f) - 1.0f);
+    }
+    reinterpret_cast<float*>(smem)[i] = v;
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < SG_STAGES; ++s) mbar_init(&done[s], 1);
     abort_flag = 0;
@@ -479,7 +492,8 @@ __global__ void __launch_bounds__(64, 1) tf32_peak_kernel(int stages, int* statu
 
 }  // namespace
 
-cudaError_t launch_tf32_peak(int stages, int blocks, int* status, cudaStream_t stream) {
+cudaError_t launch_tf32_peak(int stages, int blocks, bool random_operands, int* status,
+                             cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(tf32_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -487,7 +501,8 @@ cudaError_t launch_tf32_peak(int stages, int blocks, int* status, cudaStream_t s
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  tf32_peak_kernel<<<blocks, 64, SG_STAGE_BYTES + 256, stream>>>(stages, status);
+  tf32_peak_kernel<<<blocks, 64, SG_STAGE_BYTES + 256, stream>>>(stages, random_operands ? 1 : 0,
+                                                                 status);
   return cudaGetLastError();
 }
 

@@ -65,7 +65,10 @@ cudaError_t launch_sgemm_tile(const SgemmArgs& args, int sm_count, cudaStream_t 
 // Tensor-pipe throughput loop of the GEMM kernel's MMA shape on shared-memory-resident
 // operands: every block issues `stages` x 6 tcgen05.mma.kind::tf32 of 128 x 256 x 8
 // (2 * 128 * 256 * 8 flop each). `status` receives a KERR_* code if a wait gives up.
-cudaError_t launch_tf32_peak(int stages, int blocks, int* status, cudaStream_t stream);
+// `random_operands`: fill the stage with TF32-exact uniform(-1, 1) values instead of ones, so
+// that the figure includes what the board's power limit does to a real product.
+cudaError_t launch_tf32_peak(int stages, int blocks, bool random_operands, int* status,
+                             cudaStream_t stream);
 constexpr double SG_PEAK_FLOP_PER_STAGE = 6.0 * 2.0 * SG_BM * SG_BN * 8;
 
 // Opt the kernels into their dynamic shared memory size; once per device.

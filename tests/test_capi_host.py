@@ -306,6 +306,8 @@ def test_packaged_database_is_complete_for_an_eight_gpu_box(pl):
     tf32 = float((proc / "tf32_tensor_peak_dev-0.log").read_text())
     assert 30.0 < fp64 < 45.0            # TFLOP/s, DMMA register loop
     assert 900.0 < tf32 < 1300.0         # TFLOP/s, tcgen05 kind::tf32 issue rate
+    tf32_real = float((proc / "tf32_tensor_peak_random_dev-0.log").read_text())
+    assert 600.0 < tf32_real <= tf32     # the same loop on random operands, under the power limit
     agg = (proc / "Host-Link-Aggregate.log").read_text().split()
     assert {"H2D", "D2H", "BIDIR"} <= set(agg)
     locs = [-1] + list(range(8))
