@@ -503,6 +503,21 @@ static double block_exec_time(const GemmModelInput& in, int64_t T, double mloc, 
   return t;
 }
 
+int64_t count_enqueue_ops(const GemmModelInput& in, int64_t Mt, int64_t Nt, int64_t Kt, int d1,
+                          int d2, int n_active) {
+  // launches per C tile: the first covers one k tile, the rest chains of four
+  const int64_t per_ctile = Kt <= 0 ? 1 : 1 + (Kt - 1 + 3) / 4;
+  int64_t ops = Mt * Nt * per_ctile;
+  const int64_t kt = std::max<int64_t>(Kt, 0);
+  const int a_cons = n_active > 1 ? d2 : 1, b_cons = n_active > 1 ? d1 : 1;
+  // a tile on a GPU is read in place by that GPU (FP64) or packed from where it lies (FP32)
+  ops += Mt * kt * a_cons - (in.locA >= 0 ? Mt * kt / std::max(d1, 1) : 0);
+  ops += kt * Nt * b_cons - (in.locB >= 0 ? kt * Nt / std::max(d2, 1) : 0);
+  const int64_t c_moves = (in.beta_nonzero ? 2 : 1) * Mt * Nt;
+  ops += in.locC >= 0 ? c_moves - c_moves / std::max(n_active, 1) : c_moves;
+  return ops;
+}
+
 double predict_gemm(const GemmModelInput& in, int64_t T, const std::vector<int>& units,
                     const double sl[6], std::vector<UnitPrediction>* per_unit) {
   (void)sl;   // the reference's score is reported, not applied: its terms are modelled here
@@ -547,9 +562,11 @@ double predict_gemm(const GemmModelInput& in, int64_t T, const std::vector<int>&
     else if (in.locB != dev) { peer_in += panelB; }
     if (in.locC == -1) { host_in += blockC * inC; host_out += blockC; }
     else if (in.locC != dev) { peer_in += blockC * inC; }
-    // an operand that lives on one GPU leaves it once per unit that reads it
-    if (in.locA >= 0) src_out = std::max(src_out, panelA * (n_active - (in.locA == dev ? 1 : 0)));
-    if (in.locB >= 0) src_out = std::max(src_out, panelB * (n_active - (in.locB == dev ? 1 : 0)));
+    // an operand that lives on one GPU leaves it once per unit that reads it; two operands
+    // on the same GPU leave through the same links
+    const double outA = in.locA >= 0 ? panelA * (n_active - (in.locA == dev ? 1 : 0)) : 0.0;
+    const double outB = in.locB >= 0 ? panelB * (n_active - (in.locB == dev ? 1 : 0)) : 0.0;
+    src_out = (in.locA >= 0 && in.locA == in.locB) ? outA + outB : std::max(outA, outB);
     const bool both = !defer && host_in > 0 && host_out > 0;
     p.t_recv = host_link_time_shared(dev, true, host_in, n_active, both, &units);
     p.t_send = host_link_time_shared(dev, false, host_out, n_active, both, &units);
@@ -576,7 +593,11 @@ double predict_gemm(const GemmModelInput& in, int64_t T, const std::vector<int>&
     worst = std::max(worst, p.t_total);
     if (per_unit) per_unit->push_back(p);
   }
-  return worst;
+  // the host side of the call
+  const int64_t Kt = in.K > 0 ? cdiv(in.K, T) : 0;
+  const double ops = (double)count_enqueue_ops(in, Mt, Nt, Kt, d1, d2, n_active);
+  const TuneConstants& c = g_consts;
+  return worst + c.call_fixed_s + c.enqueue_op_s * ops / std::max(in.enqueue_threads, 1);
 }
 
 int64_t optimize_tile_model(const GemmModelInput& in, const std::vector<int>& units,
@@ -584,14 +605,14 @@ int64_t optimize_tile_model(const GemmModelInput& in, const std::vector<int>& un
   const int U = (int)units.size();
   const int64_t min_dim = std::min(in.M, std::min(in.N, in.K));
   const std::map<int64_t, double>* curve = exec_curve(in.func, in.ta, in.tb);
-  if (!curve) {
-    const int64_t T = optimize_tile(in.M, in.N, in.K, U, c, c.tile_step, sl);
-    if (pred) *pred = predict_gemm(in, T, units, sl, nullptr);
-    return T;
-  }
   std::vector<int64_t> cands;
-  for (const auto& kv : *curve)
-    if (kv.first <= min_dim && kv.first % 16 == 0) cands.push_back(kv.first);
+  if (curve)
+    for (const auto& kv : *curve)
+      if (kv.first <= min_dim && kv.first % 16 == 0) cands.push_back(kv.first);
+  // plus a plain ladder of tile edges (the lookup interpolates between measured sizes), so
+  // that a sparse or missing table does not restrict the choice
+  for (int64_t T = 256; T <= std::min<int64_t>(min_dim, 8192); T += 256)
+    if (std::find(cands.begin(), cands.end(), T) == cands.end()) cands.push_back(T);
   // the smallest dimension as one tile edge (a tile that is not the whole problem has to be
   // a multiple of the 16-deep pipeline stage)
   if (cands.empty() || (min_dim % 16 == 0 && min_dim <= 8192 &&

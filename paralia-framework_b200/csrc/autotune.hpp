@@ -34,6 +34,14 @@ struct TuneConstants {
   // Tile edges this build considers: multiples of tile_step (TMA rows are 16 elements
   // wide; CTA tiles are 128 wide), or the whole smallest dimension.
   int64_t tile_step = 128;
+  // Host side of a call, measured on an 8 x B200 box with one thread driving all GPUs
+  // (70-problem placement sweep): a fixed part (set-up, start and end events, the join) and a
+  // part per enqueued operation (a tile kernel launch with its event waits, or a tile copy
+  // with its event record). The executor enqueues just in time, so this time adds to the
+  // device time instead of hiding under it; it is what makes small tiles expensive on
+  // millisecond-sized problems.
+  double call_fixed_s = 0.5e-3;
+  double enqueue_op_s = 2.8e-6;
 };
 
 // t = ti + tb*bytes (CoModel.cpp:108-117) plus how much slower the link gets while
@@ -110,11 +118,18 @@ struct GemmModelInput {
   int locA, locB, locC;   // -1 host, >=0 GPU
   bool beta_nonzero = true;
   const char* func;       // "Dgemm" / "Sgemm"
+  int enqueue_threads = 1;   // host threads that enqueue (one per rank in a process group)
 };
 
 struct UnitPrediction {
   double t_exec, t_recv, t_send, t_extra, t_fill, t_drain, t_total;
 };
+
+// Operations the host enqueues for a problem cut into Mt x Nt x Kt tiles on a d1 x d2 device
+// grid: tile kernel launches (the k chains of plan.hpp) and tile copies (every consumer of an
+// A or B tile gets its own copy unless the tile already lives on it; C tiles in and out).
+int64_t count_enqueue_ops(const GemmModelInput& in, int64_t Mt, int64_t Nt, int64_t Kt, int d1,
+                          int d2, int n_active);
 
 // Seconds one tile GEMM of edge T takes on a GPU (lookup with cubic extrapolation,
 // GPUexec_lookup.cpp:103-129).

@@ -846,6 +846,7 @@ int run_gemm(char TransA, char TransB, int64_t M, int64_t N, int64_t K, T alpha,
       GemmModelInput whole = mi_in;
       whole.M = M * gd1;
       whole.N = N * gd2;
+      whole.enqueue_threads = grp->world();   // every rank enqueues its own block
       paralia_ctl all = eff_ctl;
       all.active_unit_num = std::min(grp->world(), PARALIA_MAX_UNITS);
       for (int i = 0; i < all.active_unit_num; ++i) all.active_unit_id_list[i] = i;

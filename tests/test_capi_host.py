@@ -243,10 +243,19 @@ def test_database_round_trip(pl, tmp_path):
         "".join(f"{k} {n} 1.0e+06\n" for k in ("H2D", "D2H", "BIDIR") for n in (1, 8)))
     pl.load_database(str(tmp_path))
     try:
+        auto = pl.autotune_gemm(8, "N", "N", 32768, 32768, 32768, -1, -1, -1,
+                                pl.make_ctl(units=list(range(8))))
+        # the same rate at every tile size: fill and drain favour small tiles, the host's cost
+        # per enqueued launch and copy favours large ones; the arg-min lies in between
+        assert 1024 < auto.T < 8192
         rep = pl.autotune_gemm(8, "N", "N", 32768, 32768, 32768, -1, -1, -1,
-                               pl.make_ctl(units=list(range(8))))
-        # the same rate at every tile size: the smallest tile wins (least fill and drain)
+                               pl.make_ctl(T=1024, units=list(range(8))))
         assert rep.T == 1024 and (rep.grid_d1, rep.grid_d2) == (2, 4)
+        assert auto.pred_t < rep.pred_t
+        # host side of the call: a fixed part and 2.8 us per launch or tile copy. 32 x 32 C tiles
+        # with 1 + 8 launches each; every A tile goes to the 4 GPUs of a grid row, every B tile
+        # to the 2 GPUs of a grid column, every C tile in and out
+        t_host = 0.5e-3 + 2.8e-6 * (1024 * 9 + 32 * 32 * 4 + 32 * 32 * 2 + 2 * 1024)
         tile = 1024 * 1024 * 8
         t_exec = (16384 / 1024) * (8192 / 1024) * 32 * (2.0 * 1024 ** 3 / rate)
         # per GPU: a quarter of its A row panel, half of its B column panel, its C block
@@ -256,18 +265,18 @@ def test_database_round_trip(pl, tmp_path):
         # links on a 2 x 4 grid) and its GPU -> GPU forward, the last band's two C tiles out
         t_fill = (1e-5 + 2e-11 * tile) + (10e-6 + tile / 700e9)
         t_drain = 1e-5 + 2e-11 * 2 * tile
-        assert rep.pred_t == pytest.approx(t_fill + t_exec + t_drain, rel=1e-6)
+        assert rep.pred_t == pytest.approx(t_fill + t_exec + t_drain + t_host, rel=1e-6)
         # a slow host link makes the same problem link-bound
         for g in range(8):
             (proc / f"Link-Stats_loc_dest-{g}_loc_src--1.log").write_text(
                 "Intercept: 1.000000e-05\nCoefficient: 1.000000e-09\n")
         pl.load_database(str(tmp_path))
         rep2 = pl.autotune_gemm(8, "N", "N", 32768, 32768, 32768, -1, -1, -1,
-                                pl.make_ctl(units=list(range(8))))
+                                pl.make_ctl(T=1024, units=list(range(8))))
         assert rep2.T == 1024
         t_recv2 = 1e-5 + 1e-9 * 3 * 2 ** 30
         t_fill2 = (1e-5 + 1e-9 * tile) + (10e-6 + tile / 700e9)
-        assert rep2.pred_t == pytest.approx(t_recv2 + t_fill2, rel=1e-6)
+        assert rep2.pred_t == pytest.approx(t_recv2 + t_fill2 + t_host, rel=1e-6)
     finally:
         with pytest.raises(pl.ParaliaError):
             pl.load_database(str(tmp_path / "nowhere"))   # DB missing -> status, state kept
