@@ -449,12 +449,13 @@ def main():
                 # DRAM bytes per launch: algorithmic bytes of an average launch = (one A and one
                 # B tile read per (mi, ni, ki) step, plus one C tile read and written per launch,
                 # summed over the step's launches on all GPUs) / launches per step,
-                # times the 0.97 ratio of measured to algorithmic bytes from the ncu capture
+                # times the 2.03 ratio of measured to algorithmic bytes from the ncu capture
                 # of the same kernel on a small case
-                "traffic": 0.97 * 8.0 * (2.0 * float(n) ** 3 / max(rep.T, 1)
+                "traffic": 2.03 * 8.0 * (2.0 * float(n) ** 3 / max(rep.T, 1)
                                          + 2.0 * float(rep.T) ** 2 * per_step_launches) / per_step_launches,
-                "traffic_source": "algorithmic bytes x 0.97 (ncu dram__bytes of this kernel on a "
-                                  "4096^3 case, profiles/dgemm_tile_kernel_T2048_ncu_full.md)",
+                "traffic_source": "algorithmic bytes x 2.03 (ncu dram__bytes of this kernel on "
+                                  "4096-wide tiles with 4096-deep k parts, "
+                                  "profiles/dgemm_tile_kernel_T4096_ncu_full.md)",
                 "peak_source": "FP64 DMMA register-loop microbenchmark run in this process "
                                "(MEASURED_PEAKS.json holds no FP64 figure)",
                 "kernel": "dgemm_tile_kernel", "launches": launches,

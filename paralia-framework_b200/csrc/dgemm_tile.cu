@@ -97,8 +97,15 @@ __device__ __forceinline__ Item decode_item(const DgemmArgs& args, int block) {
   w.quarter = QUARTER;
   const int tile = QUARTER ? args.full_items + (block >> 2) : block;
   const int quad = QUARTER ? (block & 3) : 0;
-  // CTA tiles are numbered down the columns of C: consecutive CTAs share a slice of B
-  const int tm = tile % args.tiles_m, tn = tile / args.tiles_m;
+  // CTA tiles are numbered in panels of DG_PANEL tile columns, inside a panel along the rows
+  // of C first: the 148 CTAs resident at one time then read about twelve 128-row slices of A
+  // and twelve 128-column slices of B (100 MB at k = 4096, which the L2 holds) instead of
+  // every slice of A and five of B
+  const int per_panel = args.tiles_m * DG_PANEL;
+  const int panel = tile / per_panel;
+  const int width = min(DG_PANEL, args.tiles_n - panel * DG_PANEL);
+  const int r = tile - panel * per_panel;
+  const int tm = r / width, tn = panel * DG_PANEL + r % width;
   w.qm = quad & 1;
   w.qn = quad >> 1;
   w.tm0 = tm * DG_BM;
@@ -612,6 +619,7 @@ cudaError_t launch_dgemm_tile(const CUtensorMap& mapA, const CUtensorMap& mapB,
   DgemmArgs args = args_in;
   dgemm_tile_schedule(args.M, args.N, current_sm_count(), args.lone != 0, &args.tiles_m,
                       &args.full_items, &args.quarter_items);
+  args.tiles_n = (args.N + DG_BN - 1) / DG_BN;
   if (args.full_items + args.quarter_items <= 0) return cudaSuccess;
   if (a_kcontig)
     return b_kcontig ? launch_pair<true, true>(mapA, mapB, args, stream)

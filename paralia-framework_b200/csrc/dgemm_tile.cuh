@@ -30,6 +30,7 @@ constexpr int DG_FOLD_LAG = 2;  // fold: a stage is refilled this many iteration
 constexpr int DG_STAGE_BYTES = (DG_BM + DG_BN) * DG_BK * 8;
 constexpr int DG_SMEM_BYTES = DG_STAGES * DG_STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 constexpr int DG_MAX_PARTS = 64;
+constexpr int DG_PANEL = 12;    // tile columns per panel of the CTA tile numbering
 
 // One slice of the K loop: where the A and B tiles of that slice start inside the
 // tensors their TMA maps describe. (row, k, z) for A and (k, col, z) for B are logical
@@ -53,8 +54,8 @@ struct DgemmArgs {
                         // round of CTA tiles is cut into quarter items
   // Work items of the launch, filled in by launch_dgemm_tile (dgemm_tile_schedule):
   // items [0, full_items) are 128 x 128 CTA tiles, the next quarter_items are 64 x 64
-  // quarters of the CTA tiles that follow; tiles_m = CTA tiles per column of C.
-  int32_t tiles_m, full_items, quarter_items;
+  // quarters of the CTA tiles that follow; tiles_m / tiles_n = CTA tiles per column / row of C.
+  int32_t tiles_m, tiles_n, full_items, quarter_items;
   DgemmKPart parts[DG_MAX_PARTS];
 };
 
